@@ -3,7 +3,7 @@
 Per cache group one tensor [num_pages + 1, page_elems]: page 0 is the null page (real memory,
 never handed out). A page holds, for each member layer of the group, K then V for `page_size`
 tokens, each laid out [kv_head][offset][head_dim] (values with a head size of their own where a
-layer has one), so a (page, head) tile is contiguous. One
+layer has one; no V at all for a member whose values lie inside its key rows), so a (page, head) tile is contiguous. One
 block table per request and group therefore serves all the group's layers (the reference packs
 all layers of a group into one page row too: kelpie-models/kelpie_models/sdk/kv.py:1-34,
 118-143). Per-request state of fixed size lives beside it: one tensor [max_requests, *shape]
@@ -22,17 +22,23 @@ from .manager import GroupSpec
 @dataclass(frozen=True)
 class MemberSpec:
     """What one layer's cache needs: a group (by window and kept first tokens) and the sizes of a
-    token's K and V (`v_head_dim` 0: values have the keys' head size)."""
+    token's K and V (`v_head_dim` 0: values have the keys' head size). `values_in_keys`: a token's value is the first
+    v_head_dim numbers of its key row (a cache of latents): the pages hold key rows only."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
     keep_first: int = 0
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim or self.head_dim
+
+    @property
+    def stored_value_dim(self) -> int:
+        return 0 if self.values_in_keys else self.value_dim
 
     @property
     def lifetime(self) -> tuple[int, int]:
@@ -80,7 +86,7 @@ class KVArena:
         offsets = []
         for m, g in zip(members, member_group):
             k_elems = m.n_kv_heads * groups[g].page_size * m.head_dim
-            v_elems = m.n_kv_heads * groups[g].page_size * m.value_dim
+            v_elems = m.n_kv_heads * groups[g].page_size * m.stored_value_dim
             offsets.append((sizes[g], sizes[g] + k_elems))
             sizes[g] += k_elems + v_elems
         self.tensors = [
@@ -91,7 +97,7 @@ class KVArena:
         for (k_off, v_off), m, g in zip(offsets, members, member_group):
             flat = self.tensors[g].view(-1)
             self.members.append(CacheMember(
-                group=g, k=flat[k_off:], v=flat[v_off:], page_stride=sizes[g], page_size=groups[g].page_size,
+                group=g, k=flat[k_off:], v=flat[k_off if m.values_in_keys else v_off:], page_stride=sizes[g], page_size=groups[g].page_size,
                 n_pages=groups[g].num_pages + 1, n_kv_heads=m.n_kv_heads, head_dim=m.head_dim, window=m.window,
                 v_head_dim=m.v_head_dim, keep_first=m.keep_first,
             ))

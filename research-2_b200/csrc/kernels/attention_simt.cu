@@ -7,7 +7,8 @@
 // the head size, never on how the step was cut or batched, so a row's output is the same bits
 // whichever batch it came in. It also takes what the fast kernels leave out: a value head size that
 // differs from the key's, a window that keeps a sequence's first keys, a sink in the softmax's
-// denominator, and an output gate.
+// denominator, an output gate, and values that are the first numbers of the key rows themselves (a
+// cache of latents: the value pointer is the key pointer and a value row is as long as a key row).
 //
 // Reference formulas: kelpie-models/kelpie_models/kernels/ops/paged_attention.py:160-240
 // (scores * scale 179, visibility 186-212, softmax 215-240, PV 182-183, pad rows zero 140).
@@ -29,7 +30,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
                       const int32_t* __restrict__ seq_lens, int n_heads, int n_kv_heads, int head_dim, int v_head_dim,
                       float scale, int window, int keep_first, int sink, const T* __restrict__ gate, int gate_row_stride,
                       int n_pages, float softcap, const float* __restrict__ sinks, const float* __restrict__ head_gate,
-                      int head_gate_stride) {
+                      int head_gate_stride, int v_row_stride) {
   pdl_launch_dependents();  // the next kernel may begin its prologue
   pdl_wait();               // the previous kernel's writes are visible from here on
   __shared__ float q_s[WARPS][MAX_HEAD_DIM];
@@ -62,7 +63,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
 #pragma unroll
   for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) acc[i] = 0.f;
   const size_t k_head_off = size_t(kvh) * page_size * head_dim;
-  const size_t v_head_off = size_t(kvh) * page_size * v_head_dim;
+  const size_t v_head_off = size_t(kvh) * page_size * v_row_stride;
 
   for (int range = 0; range < 2; ++range) {
     const int lo = range == 0 ? 0 : first, hi = range == 0 ? kept - 1 : last;
@@ -92,7 +93,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
         int key = j0 + jj;
         int page = table[key / page_size];
         page = (page < 0 || page >= n_pages) ? 0 : page;
-        const T* vr = v_cache + size_t(page) * page_stride + v_head_off + size_t(key % page_size) * v_head_dim;
+        const T* vr = v_cache + size_t(page) * page_stride + v_head_off + size_t(key % page_size) * v_row_stride;
 #pragma unroll
         for (int i = 0; i < MAX_HEAD_DIM / 32; ++i) {
           int d = lane + 32 * i;
@@ -124,7 +125,9 @@ attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__
 // `sink` adds one to the softmax's denominator; `gate` (may be null; [T, n_heads * v_head_dim] with its
 // own row stride) multiplies the output by its sigmoid. `softcap` > 0 caps the scaled scores (cap * tanh(s / cap));
 // `sinks` (may be null; float [n_heads]) puts exp(sinks[h]) into head h's denominator; `head_gate` (may be null; float
-// [T, n_heads] with its own row stride) multiplies head h's output by the sigmoid of its entry.
+// [T, n_heads] with its own row stride) multiplies head h's output by the sigmoid of its entry. `v_row_stride` (0: v_head_dim)
+// is the length of a value row in the cache: with v_cache = k_cache and v_row_stride = head_dim the values are the first
+// v_head_dim numbers of the keys.
 extern "C" int r2_attention_simt(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
                                  const void* v_cache, long long page_stride, int page_size,
                                  const int32_t* block_tables, int table_width, const int32_t* row_entry,
@@ -132,21 +135,23 @@ extern "C" int r2_attention_simt(const void* q, int q_row_stride, void* out, int
                                  int n_kv_heads, int head_dim, int v_head_dim, float scale, int window, int keep_first,
                                  int sink, const void* gate, int gate_row_stride, int n_pages, int dtype,
                                  float softcap, const float* sinks, const float* head_gate, int head_gate_stride,
-                                 cudaStream_t stream) {
+                                 int v_row_stride, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (head_dim < 1 || head_dim > MAX_HEAD_DIM || v_head_dim < 1 || v_head_dim > MAX_HEAD_DIM) return R2_UNSUPPORTED;
   if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0 || keep_first < 0) return R2_BAD_SHAPE;
+  if (v_row_stride <= 0) v_row_stride = v_head_dim;   // values in rows of their own
+  if (v_row_stride < v_head_dim) return R2_BAD_SHAPE;
   dim3 grid(n_rows, (n_heads + WARPS - 1) / WARPS);
   if (dtype == R2_F32) {
     r2_launch(attention_simt_kernel<float>, dim3(grid), dim3(WARPS * 32), size_t(0), stream,
         (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_cache, (const float*)v_cache,
         page_stride, page_size, block_tables, table_width, row_entry, positions, seq_lens, n_heads, n_kv_heads,
-        head_dim, v_head_dim, scale, window, keep_first, sink, (const float*)gate, gate_row_stride, n_pages, softcap, sinks, head_gate, head_gate_stride);
+        head_dim, v_head_dim, scale, window, keep_first, sink, (const float*)gate, gate_row_stride, n_pages, softcap, sinks, head_gate, head_gate_stride, v_row_stride);
   } else if (dtype == R2_BF16) {
     r2_launch(attention_simt_kernel<bf16>, dim3(grid), dim3(WARPS * 32), size_t(0), stream,
         (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_cache, (const bf16*)v_cache,
         page_stride, page_size, block_tables, table_width, row_entry, positions, seq_lens, n_heads, n_kv_heads,
-        head_dim, v_head_dim, scale, window, keep_first, sink, (const bf16*)gate, gate_row_stride, n_pages, softcap, sinks, head_gate, head_gate_stride);
+        head_dim, v_head_dim, scale, window, keep_first, sink, (const bf16*)gate, gate_row_stride, n_pages, softcap, sinks, head_gate, head_gate_stride, v_row_stride);
   } else {
     return R2_BAD_DTYPE;
   }

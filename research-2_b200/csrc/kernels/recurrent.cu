@@ -1,5 +1,7 @@
 // Mixers that carry a state of fixed size from token to token instead of a cache that grows: a matrix
-// memory with exponential gates (mLSTM) and a state-space layer (Mamba-2's recurrence), both of the form
+// memory with exponential gates (mLSTM), a state-space layer (Mamba-2's recurrence) and retention (linear attention
+// with one fixed decay per head, keep_t = decay and take_t = 1; its queries and keys are rotated by position on their way
+// into shared memory, in float, so what enters the recurrence is never rounded to 16 bits), all of the form
 //
 //     S_t = keep_t * S_(t-1) + take_t * w_t v_t^T        S: [rows x columns] per head, float
 //     y_t = S_t^T r_t  (+ what the layer adds)
@@ -27,7 +29,7 @@ namespace {
 constexpr int MAX_TILE = 32, SMALL_TILE = 4;
 constexpr int NORM_COPIES = 8;  // copies of a matrix memory's normaliser and maximum: one per slice of the columns at most
 
-constexpr int MODE_MLSTM = 0, MODE_SSD = 1;
+constexpr int MODE_MLSTM = 0, MODE_SSD = 1, MODE_DECAY = 2;
 
 __device__ __forceinline__ float soft_cap(float x, float cap) { return cap > 0.f ? cap * tanhf(x / cap) : x; }
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
@@ -44,6 +46,10 @@ struct ScanArgs {
   const float* skip;                     // state space, per head: y += skip * v
   float cap;                             // mLSTM: gates are cap * tanh(x / cap); 0 = no cap
   float read_scale;                      // r is multiplied by it
+  float write_scale;                     // retention: w is multiplied by it (after the rotation)
+  const float* decay;                    // retention, per head: keep
+  const float* inv_freq; int rot_half;   // retention: of r and w the first 2 * rot_half dimensions turn, dimension i with
+  const int32_t* positions;              // i + rot_half, by the angle positions[row] * inv_freq[i] (rot_half 0: no rotation)
   float* state; long long slot_stride;   // per request slot; per head: S [rows][cols] (+ mLSTM: NORM_COPIES times n [rows], m)
   int head_stride;
   const int32_t* q_start; const int32_t* state_slot; const int32_t* fresh;
@@ -124,13 +130,23 @@ outer_scan_kernel(const ScanArgs a) {
         const size_t row = size_t(t0 + tt);
         tr[u] = live ? to_float(read[row * a.read_stride + i]) : 0.f;
         tw[u] = live ? to_float(write[row * a.write_stride + i]) : 0.f;
+        if (MODE == MODE_DECAY && live && i < 2 * a.rot_half) {
+          // the pair (u, v) = (x[i], x[i + half]) becomes (u cos - v sin, v cos + u sin); position and angle are float
+          const bool low = i < a.rot_half;
+          const int other = low ? i + a.rot_half : i - a.rot_half;
+          float sn, cs;
+          sincosf(float(a.positions[row]) * a.inv_freq[low ? i : other], &sn, &cs);
+          if (low) sn = -sn;
+          tr[u] = fmaf(tr[u], cs, to_float(read[row * a.read_stride + other]) * sn);
+          tw[u] = fmaf(tw[u], cs, to_float(write[row * a.write_stride + other]) * sn);
+        }
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const int idx = base + u * blockDim.x + tid;
         if (idx < nt * padded) {
           rs[idx] = tr[u] * a.read_scale;
-          ws[idx] = tw[u];
+          ws[idx] = MODE == MODE_DECAY ? tw[u] * a.write_scale : tw[u];
         }
       }
     }
@@ -148,7 +164,12 @@ outer_scan_kernel(const ScanArgs a) {
         if (idx < nt * cv) vs[idx] = tv[u];
       }
     }
-    if (tid < nt) {
+    if (MODE == MODE_DECAY) {
+      if (tid < nt) {
+        g0[tid] = 1.f;
+        g1[tid] = a.decay[h];
+      }
+    } else if (tid < nt) {
       const float* gr = a.gates + size_t(t0 + tid) * a.gates_stride;
       if (MODE == MODE_MLSTM) {
         g0[tid] = soft_cap(gr[h], a.cap);
@@ -349,8 +370,9 @@ causal_conv_kernel(const T* __restrict__ in, int in_stride, T* __restrict__ out,
 }
 
 // ---- norm over groups of columns, with a gate ---------------------------------------------------
-// One warp per (row, group). gate_first: y <- y * silu(gate), then the group's RMS norm, times weight.
-// Otherwise: the group's RMS norm, times weight, times sigmoid(gate).
+// One warp per (row, group). gate_first 1: y <- y * silu(gate), then the group's RMS norm, times weight.
+// 0: the group's RMS norm, times weight, times sigmoid(gate). 2: the group's RMS norm, times weight, times silu(gate).
+// weight may be null: a gain of one.
 template <typename T>
 __global__ void __launch_bounds__(128)
 group_norm_gated_kernel(const float* __restrict__ y, int y_stride, const T* __restrict__ gate, int gate_stride,
@@ -369,7 +391,7 @@ group_norm_gated_kernel(const float* __restrict__ y, int y_stride, const T* __re
   float sq = 0.f;
   for (int d = lane; d < group_size; d += 32) {
     float v = yr[d];
-    if (gate_first) {
+    if (gate_first == 1) {
       const float z = to_float(gr[d]);
       v *= z / (1.f + expf(-z));
     }
@@ -379,8 +401,9 @@ group_norm_gated_kernel(const float* __restrict__ y, int y_stride, const T* __re
   for (int d = lane; d < group_size; d += 32) {
     float v = yr[d];
     const float z = to_float(gr[d]);
-    if (gate_first) v = v * (z / (1.f + expf(-z))) * inv * wr[d];
-    else v = v * inv * wr[d] * (1.f / (1.f + expf(-z)));
+    const float gain = weight != nullptr ? wr[d] : 1.f;
+    if (gate_first == 1) v = v * (z / (1.f + expf(-z))) * inv * gain;
+    else v = v * inv * gain * ((gate_first == 2 ? z : 1.f) / (1.f + expf(-z)));
     o[d] = from_float<T>(v);
   }
 }
@@ -402,7 +425,7 @@ group_norm_gated_block_kernel(const float* __restrict__ y, int y_stride, const T
   float sq = 0.f;
   for (int d = threadIdx.x; d < group_size; d += blockDim.x) {
     float v = yr[d];
-    if (gate_first) {
+    if (gate_first == 1) {
       const float z = to_float(gr[d]);
       v *= z / (1.f + expf(-z));
     }
@@ -412,8 +435,9 @@ group_norm_gated_block_kernel(const float* __restrict__ y, int y_stride, const T
   for (int d = threadIdx.x; d < group_size; d += blockDim.x) {
     float v = yr[d];
     const float z = to_float(gr[d]);
-    if (gate_first) v = v * (z / (1.f + expf(-z))) * inv * wr[d];
-    else v = v * inv * wr[d] * (1.f / (1.f + expf(-z)));
+    const float gain = weight != nullptr ? wr[d] : 1.f;
+    if (gate_first == 1) v = v * (z / (1.f + expf(-z))) * inv * gain;
+    else v = v * inv * gain * ((gate_first == 2 ? z : 1.f) / (1.f + expf(-z)));
     o[d] = from_float<T>(v);
   }
 }
@@ -445,6 +469,29 @@ extern "C" int r2_mlstm_scan(const void* q, int q_stride, const void* k, int k_s
   a.heads_per_group = 1; a.rows = dim; a.cols = vdim; a.single_rows = single_rows;
   if (dtype == R2_F32) return launch_scan<float, MODE_MLSTM>(a, n_entries, n_heads, stream);
   if (dtype == R2_BF16) return launch_scan<bf16, MODE_MLSTM>(a, n_entries, n_heads, stream);
+  return R2_BAD_DTYPE;
+}
+
+// Retention: S <- decay[h] S + k v^T, o = S^T q per head, with q and k rotated by position (the first rot_dims dimensions
+// of a head, dimension i with i + rot_dims / 2, angle positions[t] * inv_freq[i]; rot_dims 0: none) and k multiplied by
+// k_scale after the rotation. q, k [T, heads * dim], v [T, heads * vdim] (slices of a projection); decay float [heads];
+// state float [slots][heads][dim][vdim]; out [T, heads * vdim] float, before the heads' norm.
+extern "C" int r2_retention_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride,
+                                 const float* decay, float k_scale, const float* inv_freq, int rot_dims, const int32_t* positions,
+                                 float* state, long long slot_stride, const int32_t* q_start, const int32_t* state_slot,
+                                 const int32_t* fresh, int n_entries, float* out, int out_stride, int n_heads, int dim, int vdim,
+                                 int single_rows, int dtype, cudaStream_t stream) {
+  if (n_entries <= 0) return R2_OK;
+  if (n_heads < 1 || dim < 1 || vdim < 1 || rot_dims < 0 || rot_dims % 2 != 0 || rot_dims > dim) return R2_BAD_SHAPE;
+  if (rot_dims > 0 && (inv_freq == nullptr || positions == nullptr)) return R2_BAD_SHAPE;
+  ScanArgs a = {};
+  a.read = q; a.read_stride = q_stride; a.write = k; a.write_stride = k_stride; a.value = v; a.value_stride = v_stride;
+  a.read_scale = 1.f; a.write_scale = k_scale; a.decay = decay; a.inv_freq = inv_freq; a.rot_half = rot_dims / 2; a.positions = positions;
+  a.state = state; a.slot_stride = slot_stride; a.head_stride = dim * vdim;
+  a.q_start = q_start; a.state_slot = state_slot; a.fresh = fresh; a.out = out; a.out_stride = out_stride;
+  a.heads_per_group = 1; a.rows = dim; a.cols = vdim; a.single_rows = single_rows;
+  if (dtype == R2_F32) return launch_scan<float, MODE_DECAY>(a, n_entries, n_heads, stream);
+  if (dtype == R2_BF16) return launch_scan<bf16, MODE_DECAY>(a, n_entries, n_heads, stream);
   return R2_BAD_DTYPE;
 }
 

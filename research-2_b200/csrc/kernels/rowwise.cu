@@ -736,3 +736,117 @@ extern "C" int r2_pair_norm_add(const float* x, const float* a, const float* b, 
   r2_launch(pair_norm_add_kernel, dim3(n_rows), dim3(256), size_t(0), stream, x, a, b, wa, wb, out, width, eps, share);
   return launch_status();
 }
+
+// ---- a sublayer's output, normalised, joins the stream (and the next sublayer's input leaves with it) --------------
+// out = x + y / rms(y) * w, all float; with `next_w` also h = out / rms(out) * next_w in the compute dtype: the norm after a
+// sublayer, the residual sum and the norm before the next sublayer in one pass. One CTA per row; the row stays in
+// registers between the passes (ROWS_PER_THREAD elements a thread) where it fits, else it is read again.
+namespace {
+constexpr int NORM_ADD_THREADS = 256, NORM_ADD_KEEP = 8;
+
+template <typename O>
+__global__ void __launch_bounds__(NORM_ADD_THREADS)
+norm_add_kernel(const float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ out,
+                const float* __restrict__ next_w, O* __restrict__ next, int width, float eps, float next_eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t at = size_t(blockIdx.x) * width;
+  const bool fits = width <= NORM_ADD_THREADS * NORM_ADD_KEEP;
+  float keep[NORM_ADD_KEEP];
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_ADD_KEEP; ++i) {
+    const int d = threadIdx.x + i * NORM_ADD_THREADS;
+    keep[i] = (fits && d < width) ? y[at + d] : 0.f;
+    sq = fmaf(keep[i], keep[i], sq);
+  }
+  if (!fits)
+    for (int d = threadIdx.x; d < width; d += NORM_ADD_THREADS) sq = fmaf(y[at + d], y[at + d], sq);
+  const float inv = 1.f / sqrtf(block_sum(sq, scratch) / float(width) + eps);
+  float sq_out = 0.f;
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < NORM_ADD_KEEP; ++i) {
+      const int d = threadIdx.x + i * NORM_ADD_THREADS;
+      if (d < width) {
+        keep[i] = x[at + d] + keep[i] * inv * w[d];
+        out[at + d] = keep[i];
+        sq_out = fmaf(keep[i], keep[i], sq_out);
+      }
+    }
+  } else {
+    for (int d = threadIdx.x; d < width; d += NORM_ADD_THREADS) {
+      const float v = x[at + d] + y[at + d] * inv * w[d];
+      out[at + d] = v;
+      sq_out = fmaf(v, v, sq_out);
+    }
+  }
+  if (next == nullptr) return;
+  const float inv_out = 1.f / sqrtf(block_sum(sq_out, scratch) / float(width) + next_eps);
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < NORM_ADD_KEEP; ++i) {
+      const int d = threadIdx.x + i * NORM_ADD_THREADS;
+      if (d < width) next[at + d] = from_float<O>(keep[i] * inv_out * next_w[d]);
+    }
+  } else {
+    for (int d = threadIdx.x; d < width; d += NORM_ADD_THREADS) next[at + d] = from_float<O>(out[at + d] * inv_out * next_w[d]);
+  }
+}
+
+// xIELU: for z > 0, a_pos z^2 + z / 2; for z <= 0, a_neg (e^z - 1 - z) + z / 2 (a_pos, a_neg are made from the layer's two
+// learned numbers on the host). In float, rounded once on the way out.
+__device__ __forceinline__ float xielu(float z, float a_pos, float a_neg) {
+  return z > 0.f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+xielu_kernel(const T* __restrict__ in, int in_stride, T* __restrict__ out, int out_stride, int width, float a_pos, float a_neg) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const T* r = in + size_t(blockIdx.x) * in_stride;
+  T* o = out + size_t(blockIdx.x) * out_stride;
+  if (width % 2 == 0 && pair_aligned(r) && pair_aligned(o) && in_stride % 2 == 0 && out_stride % 2 == 0) {
+    for (int d = 2 * (blockIdx.y * blockDim.x + threadIdx.x); d < width; d += 2 * gridDim.y * blockDim.x) {
+      const float2 z = load2(r + d);
+      store2(o + d, xielu(z.x, a_pos, a_neg), xielu(z.y, a_pos, a_neg));
+    }
+    return;
+  }
+  for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < width; d += gridDim.y * blockDim.x)
+    o[d] = from_float<T>(xielu(to_float(r[d]), a_pos, a_neg));
+}
+}  // namespace
+
+// x, y, out float [n_rows, width] (out may be x); w float [width]. With next_w (float [width]) and next ([n_rows, width] in
+// `next_dtype`) the norm of the new stream rows is written too.
+extern "C" int r2_norm_add(const float* x, const float* y, const float* w, float* out, const float* next_w, void* next,
+                           int n_rows, int width, float eps, float next_eps, int next_dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return R2_OK;
+  if (width < 1) return R2_BAD_SHAPE;
+  if (next != nullptr && next_w == nullptr) return R2_BAD_SHAPE;
+  if (next == nullptr || next_dtype == R2_F32) {
+    r2_launch(norm_add_kernel<float>, dim3(n_rows), dim3(NORM_ADD_THREADS), size_t(0), stream, x, y, w, out, next_w, (float*)next, width, eps, next_eps);
+  } else if (next_dtype == R2_BF16) {
+    r2_launch(norm_add_kernel<bf16>, dim3(n_rows), dim3(NORM_ADD_THREADS), size_t(0), stream, x, y, w, out, next_w, (bf16*)next, width, eps, next_eps);
+  } else {
+    return R2_BAD_DTYPE;
+  }
+  return launch_status();
+}
+
+extern "C" int r2_xielu(const void* in, int in_stride, void* out, int out_stride, int n_rows, int width, float a_pos, float a_neg,
+                        int dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || width <= 0) return R2_OK;
+  dim3 grid(n_rows, (width + 2047) / 2048);
+  if (dtype == R2_F32) {
+    r2_launch(xielu_kernel<float>, grid, dim3(256), size_t(0), stream, (const float*)in, in_stride, (float*)out, out_stride, width, a_pos, a_neg);
+  } else if (dtype == R2_BF16) {
+    r2_launch(xielu_kernel<bf16>, grid, dim3(256), size_t(0), stream, (const bf16*)in, in_stride, (bf16*)out, out_stride, width, a_pos, a_neg);
+  } else {
+    return R2_BAD_DTYPE;
+  }
+  return launch_status();
+}

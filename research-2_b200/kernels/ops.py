@@ -143,7 +143,8 @@ def _lib(source: str) -> C.CDLL:
 def build_all(head_dims=()) -> None:
     """Compile every kernel library that does not depend on a model, and the attention kernels
     for the given head sizes (a model compiles its own head size at first use otherwise)."""
-    for source in ("rowwise", "recurrent", "routing", "gemm_simt", "gemm_tc", "attention_simt", "attention_prefill_tc", "sampling", "wait_selftest"):
+    for source in ("rowwise", "recurrent", "routing", "gemm_simt", "gemm_tc", "attention_simt", "attention_prefill_tc", "latent_attention",
+                   "sampling", "wait_selftest"):
         _lib(source)
     kernel_library("sfu_probe")  # (profiling/sfu_probe.py: a measurement, no part of a step)
     for head_dim in head_dims:
@@ -476,17 +477,18 @@ def gated_act(gate_up: torch.Tensor, limit: float, alpha: float, up_offset: floa
 
 def expert_act(gate_up: torch.Tensor, kind: str, limit: float = 0.0, alpha: float = 1.0, up_offset: float = 0.0,
                route: torch.Tensor | None = None, n_experts: int = 0, expert_width: int = 0, tail_limit: float | None = None,
-               out: torch.Tensor | None = None) -> torch.Tensor:
+               out: torch.Tensor | None = None, tail_gate: torch.Tensor | None = None) -> torch.Tensor:
     """The inner activation of gated feed-forwards whose projections lie side by side: a row of `gate_up` [T, 2 F] holds
     the gates of all F columns and then their ups. kind "relu": relu(g) * u. kind "clamped_swish": g' sigmoid(alpha g')
-    (u' + up_offset) with g' = min(g, limit), u' = clamp(u, -limit, limit). With `route` (float32 [T, n_experts], zero
+    (u' + up_offset) with g' = min(g, limit), u' = clamp(u, -limit, limit). kind "silu": g sigmoid(g) * u. With `route` (float32 [T, n_experts], zero
     for experts that a row does not use) the first n_experts * expert_width columns are the routed experts', each
     multiplied by the row's weight for its expert; the columns after them belong to an expert that every row uses
-    (limit `tail_limit`). -> [T, F] in the same dtype."""
+    (limit `tail_limit`), multiplied by sigmoid(tail_gate[row]) where `tail_gate` (float32 [T] or [T, 1], the gate's logit)
+    is given. -> [T, F] in the same dtype."""
     _need(gate_up, "gate_up", dim=2)
     if gate_up.shape[1] % 2:
         raise KernelError(f"expert_act: {tuple(gate_up.shape)} does not hold a gate and an up half")
-    kinds = {"clamped_swish": 0, "relu": 1}
+    kinds = {"clamped_swish": 0, "relu": 1, "silu": 2}
     if kind not in kinds:
         raise KernelError(f"expert_act: unknown kind {kind!r}; known: {sorted(kinds)}")
     inner = gate_up.shape[1] // 2
@@ -496,12 +498,18 @@ def expert_act(gate_up: torch.Tensor, kind: str, limit: float = 0.0, alpha: floa
             raise KernelError(f"expert_act: route {tuple(route.shape)} does not fit {n_experts} experts of {expert_width} in {inner} columns")
     else:
         n_experts = 0
+    tail_gate_stride = 0
+    if tail_gate is not None:
+        _need(tail_gate, "tail_gate", torch.float32)
+        if tail_gate.shape[0] != gate_up.shape[0] or tail_gate.numel() != gate_up.shape[0]:
+            raise KernelError(f"expert_act: tail_gate {tuple(tail_gate.shape)} is not one number per row")
+        tail_gate_stride = tail_gate.stride(0) if gate_up.shape[0] > 1 else 1
     if out is None:
         out = torch.empty(gate_up.shape[0], inner, dtype=gate_up.dtype, device=gate_up.device)
     status = _lib("routing").r2_expert_act(
         _p(gate_up), _rows(gate_up, "gate_up"), _p(out), _rows(out, "out"), gate_up.shape[0], inner, kinds[kind],
         C.c_float(limit), C.c_float(alpha), C.c_float(up_offset), _p(route), n_experts, expert_width,
-        C.c_float(limit if tail_limit is None else tail_limit), dtype_code(gate_up.dtype), _stream())
+        C.c_float(limit if tail_limit is None else tail_limit), _p(tail_gate), tail_gate_stride, dtype_code(gate_up.dtype), _stream())
     _check(status, "expert_act")
     return out
 
@@ -581,6 +589,155 @@ def pair_norm_add(x: torch.Tensor, a: torch.Tensor, b: torch.Tensor, w_a: torch.
     status = _lib("rowwise").r2_pair_norm_add(_p(x), _p(a), _p(b), _p(w_a), _p(w_b), _p(out), x.shape[0], x.shape[1],
                                              C.c_float(eps), C.c_float(share), _stream())
     _check(status, "pair_norm_add")
+    return out
+
+
+def norm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, next_weight: torch.Tensor | None = None,
+             next_eps: float = 0.0, next_dtype: torch.dtype | None = None):
+    """x + y / rms(y) * weight, all float32 [T, D]: a sublayer's output is normalised and joins the stream. With
+    `next_weight` the same launch also gives the norm of the new stream rows, rms_norm(x_new) * next_weight in `next_dtype`
+    (the next sublayer's input): -> (x_new, h_next); else -> x_new."""
+    for name, t in (("x", x), ("y", y)):
+        _need(t, name, torch.float32, 2)
+        if t.shape != x.shape or not t.is_contiguous():
+            raise KernelError(f"norm_add: {name} {tuple(t.shape)} must be contiguous and shaped like x {tuple(x.shape)}")
+    _need(weight, "weight", torch.float32, 1)
+    if weight.shape[0] != x.shape[1]:
+        raise KernelError(f"norm_add: weight {tuple(weight.shape)} does not fit the width {x.shape[1]}")
+    out = torch.empty_like(x)
+    nxt = None
+    if next_weight is not None:
+        _need(next_weight, "next_weight", torch.float32, 1)
+        if next_weight.shape[0] != x.shape[1]:
+            raise KernelError(f"norm_add: next_weight {tuple(next_weight.shape)} does not fit the width {x.shape[1]}")
+        nxt = torch.empty(x.shape, dtype=next_dtype or torch.float32, device=x.device)
+    status = _lib("rowwise").r2_norm_add(_p(x), _p(y), _p(weight), _p(out), _p(next_weight), _p(nxt), x.shape[0], x.shape[1],
+                                        C.c_float(eps), C.c_float(next_eps), dtype_code(nxt.dtype) if nxt is not None else F32, _stream())
+    _check(status, "norm_add")
+    return out if nxt is None else (out, nxt)
+
+
+def xielu(z: torch.Tensor, a_pos: float, a_neg: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """For z > 0: a_pos z^2 + z / 2; for z <= 0: a_neg (e^z - 1 - z) + z / 2, elementwise on [T, F], computed in float32."""
+    _need(z, "z", dim=2)
+    if out is None:
+        out = torch.empty(z.shape, dtype=z.dtype, device=z.device)
+    status = _lib("rowwise").r2_xielu(_p(z), _rows(z, "z"), _p(out), _rows(out, "out"), z.shape[0], z.shape[1], C.c_float(a_pos),
+                                     C.c_float(a_neg), dtype_code(z.dtype), _stream())
+    _check(status, "xielu")
+    return out
+
+
+def route_scored(h: torch.Tensor, w: torch.Tensor, correction: torch.Tensor | None, top: int, n_groups: int = 1, keep_groups: int = 1,
+                 n_extra: int = 0):
+    """Router with sigmoid scores: logits h @ w^T in float32 (w float32 [experts + n_extra, K]); an expert is chosen by
+    sigmoid(logit) + correction, only inside the `keep_groups` best of `n_groups` equal groups of neighbouring experts (a
+    group counts by the sum of its two largest choice scores; the lower index wins ties), the `top` largest; the chosen
+    experts' weights are their sigmoids over the sum of the chosen sigmoids (+ 1e-20). The last n_extra rows of w are further
+    gates: their logits come back as they are. -> (dense float32 [T, experts]: a row's weights, zero where not chosen; chosen
+    int32 [T, top]; their weights float32 [T, top]; extra float32 [T, n_extra] or None)."""
+    _need(h, "h", dim=2)
+    _need(w, "w", torch.float32, 2)
+    e = w.shape[0] - n_extra
+    if (w.shape[1] != h.shape[1] or not w.is_contiguous() or e < 1 or n_groups < 1 or e % n_groups or not 1 <= keep_groups <= n_groups
+            or not 1 <= top <= e // n_groups * keep_groups):
+        raise KernelError(f"route_scored: h {tuple(h.shape)}, w {tuple(w.shape)}, top {top}, {keep_groups} of {n_groups} groups do not fit")
+    if correction is not None:
+        _need(correction, "correction", torch.float32, 1)
+        if correction.shape[0] != e:
+            raise KernelError(f"route_scored: correction {tuple(correction.shape)} is not [{e}]")
+    n = h.shape[0]
+    dense = torch.empty(n, e, dtype=torch.float32, device=h.device)
+    chosen = torch.empty(n, top, dtype=torch.int32, device=h.device)
+    weight = torch.empty(n, top, dtype=torch.float32, device=h.device)
+    extra = torch.empty(n, n_extra, dtype=torch.float32, device=h.device) if n_extra else None
+    status = _lib("routing").r2_route_scored(_p(h), _rows(h, "h"), _p(w), _p(correction), _p(dense), _p(chosen), _p(weight), _p(extra),
+                                            n, e, n_extra, top, n_groups, keep_groups, h.shape[1], dtype_code(h.dtype), _stream())
+    _check(status, "route_scored")
+    return dense, chosen, weight, extra
+
+
+def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, k_scale: float,
+                   inv_freq: torch.Tensor | None, rot_dims: int, positions: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
+                   state_slot: torch.Tensor, fresh: torch.Tensor, n_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """Retention's recurrence S <- decay[h] S + k v^T, o = S^T q for every entry of a batch, from and to the entries' state
+    slots. q, k [T, heads * dim], v [T, heads * vdim] (slices of a projection); the kernel rotates q and k by position on their
+    way in (of each head the first rot_dims dimensions, i with i + rot_dims / 2, angle positions[t] * inv_freq[i], in float32)
+    and multiplies k by k_scale after that. decay float32 [heads]; state float32 [slots, heads * dim * vdim].
+    -> float32 [T, heads * vdim], the heads' outputs before their norm."""
+    n = _entries(q_start, state_slot, fresh)
+    for name, t, width in (("q", q, n_heads * dim), ("k", k, n_heads * dim), ("v", v, n_heads * vdim)):
+        _need(t, name, q.dtype, 2)
+        if t.shape[1] != width or t.shape[0] != q.shape[0]:
+            raise KernelError(f"retention_scan: {name} {tuple(t.shape)} is not [T, {width}]")
+    _need(decay, "decay", torch.float32, 1)
+    _need(state, "state", torch.float32, 2)
+    _need(positions, "positions", torch.int32, 1)
+    if decay.shape[0] != n_heads or state.shape[1] != n_heads * dim * vdim or not state.is_contiguous() or positions.shape[0] < q.shape[0]:
+        raise KernelError(f"retention_scan: decay {tuple(decay.shape)} / state {tuple(state.shape)} do not fit {n_heads} heads of {dim} x {vdim}")
+    if rot_dims:
+        _need(inv_freq, "inv_freq", torch.float32, 1)
+        if rot_dims % 2 or rot_dims > dim or inv_freq.shape[0] != rot_dims // 2:
+            raise KernelError(f"retention_scan: {rot_dims} rotated dimensions of {dim}, {tuple(inv_freq.shape)} frequencies")
+    out = torch.empty(q.shape[0], n_heads * vdim, dtype=torch.float32, device=q.device)
+    status = _lib("recurrent").r2_retention_scan(
+        _p(q), _rows(q, "q"), _p(k), _rows(k, "k"), _p(v), _rows(v, "v"), _p(decay), C.c_float(k_scale), _p(inv_freq if rot_dims else None),
+        rot_dims, _p(positions), _p(state), C.c_longlong(state.shape[1]), _p(q_start), _p(state_slot), _p(fresh), n, _p(out),
+        _rows(out, "out"), n_heads, dim, vdim, int(q.shape[0] <= n), dtype_code(q.dtype), _stream())
+    _check(status, "retention_scan")
+    return out
+
+
+def latent_prepare(buf: torch.Tensor, n_heads: int, q_head_dim: int, q_rot_off: int, rot_dim: int, rot_dims: int, kv_col: int,
+                   kv_rank: int, norm_weight: torch.Tensor, eps: float, freq: torch.Tensor, magnitude: float, positions: torch.Tensor,
+                   k_cache: torch.Tensor | None = None, slot_mapping: torch.Tensor | None = None, page_size: int = 0,
+                   page_stride: int = 0, n_pages: int = 0, q_out: torch.Tensor | None = None, q_out_head_dim: int = 0,
+                   q_out_off: int = 0) -> None:
+    """In place on the rows of a stacked projection [n_heads query heads of q_head_dim | latent: kv_rank | shared key part:
+    rot_dim]: RMS norm of the latent (weight float32 [kv_rank], statistics in float32); rotation of the shared key part and of
+    every head's last-but-`q_rot_off` part (rot_dim numbers from q_rot_off on): the first rot_dims dimensions, pairs (2i, 2i + 1),
+    angle positions[t] * freq[i], cos and sin times `magnitude`. With `k_cache` the row's [latent | key part] goes to its
+    cache slot (rows of kv_rank + rot_dim numbers) in the same launch. With `q_out` ([T, n_heads * q_out_head_dim]) head h's
+    rotated part is also copied to q_out[t, h, q_out_off:]."""
+    _need(buf, "buf", dim=2)
+    _need(norm_weight, "norm_weight", torch.float32, 1)
+    _need(freq, "freq", torch.float32, 1)
+    _need(positions, "positions", torch.int32, 1)
+    if (buf.shape[1] < kv_col + kv_rank + rot_dim or kv_col < n_heads * q_head_dim or norm_weight.shape[0] != kv_rank
+            or freq.shape[0] < rot_dims // 2 or positions.shape[0] < buf.shape[0]):
+        raise KernelError(f"latent_prepare: rows of {buf.shape[1]} do not hold {n_heads} heads of {q_head_dim}, a latent of {kv_rank} and {rot_dim} more")
+    if k_cache is not None:
+        _need(slot_mapping, "slot_mapping", torch.int32, 1)
+        if k_cache.dtype != buf.dtype or slot_mapping.shape[0] < buf.shape[0]:
+            raise KernelError("latent_prepare: the cache and the projection must share a dtype, and every row needs a slot")
+    q_out_stride = 0
+    if q_out is not None:
+        _need(q_out, "q_out", buf.dtype, 2)
+        if q_out.shape != (buf.shape[0], n_heads * q_out_head_dim) or q_out_off + rot_dim > q_out_head_dim:
+            raise KernelError(f"latent_prepare: q_out {tuple(q_out.shape)} does not hold {n_heads} heads of {q_out_head_dim}")
+        q_out_stride = _rows(q_out, "q_out")
+    status = _lib("latent_attention").r2_latent_prepare(
+        _p(buf), _rows(buf, "buf"), buf.shape[0], n_heads, q_head_dim, q_rot_off, rot_dim, rot_dims, kv_col, kv_rank, _p(norm_weight),
+        C.c_float(eps), _p(freq), C.c_float(magnitude), _p(positions), _p(k_cache), _p(slot_mapping), page_size,
+        C.c_longlong(page_stride), n_pages, _p(q_out), q_out_stride, q_out_head_dim, q_out_off, dtype_code(buf.dtype), _stream())
+    _check(status, "latent_prepare")
+
+
+def head_linear(a: torch.Tensor, a_head: int, w: torch.Tensor, w_is_nk: bool, out: torch.Tensor, out_head: int, n_heads: int,
+                k: int, n: int) -> torch.Tensor:
+    """One small product per head: out[t, h * out_head: h * out_head + n] = a[t, h * a_head: h * a_head + k] @ W[h], float32
+    sums. `w` holds the heads' matrices one after the other: [n_heads * k, n] (each [k, n]; w_is_nk False) or [n_heads * n, k]
+    (each [n, k], stored [out, in]; w_is_nk True). a and out are 2-D with contiguous rows and may be wider than the heads."""
+    _need(a, "a", dim=2)
+    _need(w, "w", a.dtype, 2)
+    _need(out, "out", a.dtype, 2)
+    want = (n_heads * n, k) if w_is_nk else (n_heads * k, n)
+    if (tuple(w.shape) != want or not w.is_contiguous() or a.shape[0] != out.shape[0] or (n_heads - 1) * a_head + k > a.shape[1]
+            or (n_heads - 1) * out_head + n > out.shape[1]):
+        raise KernelError(f"head_linear: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit {n_heads} heads of {k} -> {n}")
+    status = _lib("latent_attention").r2_head_linear(_p(a), _rows(a, "a"), a_head, _p(w), int(w_is_nk), _p(out), _rows(out, "out"),
+                                                    out_head, a.shape[0], n_heads, k, n, dtype_code(a.dtype), _stream())
+    _check(status, "head_linear")
     return out
 
 
@@ -688,20 +845,23 @@ def ssd_scan(x: torch.Tensor, b: torch.Tensor, c: torch.Tensor, steps: torch.Ten
     return out
 
 
-def group_norm_gated(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, n_groups: int, eps: float, gate_first: bool,
+def group_norm_gated(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor | None, n_groups: int, eps: float, gate_first,
                      out_dtype: torch.dtype) -> torch.Tensor:
     """RMS norm of float32 rows y [T, C] in n_groups equal parts, each by its own root mean square, times weight [C], with
     a gate [T, C] (a slice of a projection, in out_dtype): `gate_first`: y * silu(gate) is what is normalised; else the
-    normalised, weighted result is multiplied by sigmoid(gate). -> [T, C] in out_dtype."""
+    normalised, weighted result is multiplied by sigmoid(gate), or, with gate_first "silu_after", by silu(gate). `weight` None:
+    a gain of one. -> [T, C] in out_dtype."""
     _need(y, "y", torch.float32, 2)
     _need(gate, "gate", out_dtype, 2)
-    _need(weight, "weight", torch.float32, 1)
-    if gate.shape != y.shape or weight.shape[0] != y.shape[1] or y.shape[1] % n_groups:
-        raise KernelError(f"group_norm_gated: y {tuple(y.shape)}, gate {tuple(gate.shape)}, weight {tuple(weight.shape)}, {n_groups} groups")
+    if weight is not None:
+        _need(weight, "weight", torch.float32, 1)
+    if gate.shape != y.shape or (weight is not None and weight.shape[0] != y.shape[1]) or y.shape[1] % n_groups:
+        raise KernelError(f"group_norm_gated: y {tuple(y.shape)}, gate {tuple(gate.shape)}, weight "
+                          f"{None if weight is None else tuple(weight.shape)}, {n_groups} groups")
     out = torch.empty(y.shape[0], y.shape[1], dtype=out_dtype, device=y.device)
     status = _lib("recurrent").r2_group_norm_gated(
         _p(y), _rows(y, "y"), _p(gate), _rows(gate, "gate"), _p(weight), _p(out), _rows(out, "out"), y.shape[0], n_groups,
-        y.shape[1] // n_groups, C.c_float(eps), int(bool(gate_first)), dtype_code(out_dtype), _stream())
+        y.shape[1] // n_groups, C.c_float(eps), 2 if gate_first == "silu_after" else int(bool(gate_first)), dtype_code(out_dtype), _stream())
     _check(status, "group_norm_gated")
     return out
 
@@ -892,7 +1052,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     window: int = 0, out: torch.Tensor | None = None, *, decode_only: bool = False,
                     max_context: int = 0, q_start: torch.Tensor | None = None, n_tiles: int = 0, v_head_dim: int = 0,
                     keep_first: int = 0, sink: bool = False, gate: torch.Tensor | None = None, softcap: float = 0.0,
-                    sinks: torch.Tensor | None = None, head_gate: torch.Tensor | None = None) -> torch.Tensor:
+                    sinks: torch.Tensor | None = None, head_gate: torch.Tensor | None = None,
+                    values_in_keys: bool = False) -> torch.Tensor:
     """Causal attention of q [T, n_heads * head_dim] over the paged cache -> [T, n_heads * v_head_dim]
     (`v_head_dim` 0: the keys' head size). With a window, `keep_first` keeps a sequence's first keys visible;
     `sink` adds one to the softmax's denominator (an extra exp(0) term: the weights sum to less than one); `gate`
@@ -900,6 +1061,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     softcap * tanh(s / softcap); `sinks` (float32 [n_heads]) puts exp(sinks[h]) into head h's denominator; `head_gate`
     (float32 [T, n_heads]) multiplies head h's output by the sigmoid of its entry: these three are taken by the general
     kernel, the mma.sync prefill kernel and the fused decode kernel.
+    `values_in_keys`: the cache holds key rows only and a key's first v_head_dim numbers are its value (a cache of
+    latents; `v_cache` is not read); the general kernel takes it.
     `decode_only` says that every row is an entry of its own (one new token each) and
     `max_context` bounds the rows' context lengths; `q_start` (int32 [R + 1]) with `n_tiles`, the
     sum over entries of ceil(rows / 64), lets the tensor-core prefill kernel take the batch. They
@@ -927,7 +1090,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     group = n_heads // max(n_kv_heads, 1)
     # only the general kernel takes a value head size of its own or a head size that is no multiple of 16; kept
     # first keys, a sink and an output gate are taken by both prefill kernels and the fused decode kernel
-    fits = v_head_dim == head_dim and head_dim % 16 == 0
+    fits = v_head_dim == head_dim and head_dim % 16 == 0 and not values_in_keys
     capped = softcap != 0.0 or sinks is not None or head_gate is not None   # what the tcgen05 kernel does not take
     head_gate_stride = 0
     if sinks is not None:
@@ -986,10 +1149,11 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _used("attention_prefill")
         return out
     status = _lib("attention_simt").r2_attention_simt(
-        _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(v_cache), C.c_longlong(page_stride),
+        _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(k_cache if values_in_keys else v_cache), C.c_longlong(page_stride),
         page_size, _p(block_tables), block_tables.shape[1], _p(row_entry), _p(positions), _p(seq_lens), n, n_heads,
         n_kv_heads, head_dim, v_head_dim, C.c_float(scale), window, keep_first, int(bool(sink)), _p(gate), gate_stride,
-        n_pages, dtype_code(q.dtype), C.c_float(softcap), _p(sinks), _p(head_gate), head_gate_stride, _stream())
+        n_pages, dtype_code(q.dtype), C.c_float(softcap), _p(sinks), _p(head_gate), head_gate_stride,
+        head_dim if values_in_keys else 0, _stream())
     _check(status, "paged_attention")
     _used("attention_simt")
     return out

@@ -71,11 +71,13 @@ class DecoderModel:
             if self.positions is not None and hasattr(mixer, "rotary") and getattr(self.positions, "rotates", False):
                 mixer.rotary = self.positions
             block_cls = registry("block")[layer.block]
+            post = {name: build_part("norm", spec, tensors, rt) for name, spec in
+                    (("post_norm_1", layer.post_norm_1), ("post_norm_2", layer.post_norm_2)) if spec is not None}
             self.blocks.append(block_cls(
                 build_part("norm", layer.norm_1, tensors, rt), mixer,
                 build_part("norm", layer.norm_2, tensors, rt) if layer.norm_2 is not None else None,
                 build_part("feed_forward", layer.feed_forward, tensors, rt) if layer.feed_forward is not None else None,
-                rt.dtype))
+                rt.dtype, **post))
         mixers = [b.mixer for b in self.blocks]
         self.schedule = spec.schedule or default_schedule(spec.layers, mixers)
         head_table = self.embedding.table if spec.head == spec.embedding else tensors[spec.head].to(rt.device, rt.dtype)
@@ -140,7 +142,8 @@ class DecoderModel:
                 total += t.numel() * t.element_size()
         add(self.embedding.table if self.head.table.data_ptr() != self.embedding.table.data_ptr() else None)
         add(self.head.table)
-        for obj in [self.head.norm] + [p for b in self.blocks for p in (b.norm_1, b.mixer, b.norm_2, b.feed_forward)]:
+        for obj in [self.head.norm] + [p for b in self.blocks for p in (b.norm_1, b.mixer, b.norm_2, b.feed_forward,
+                                                                      getattr(b, "post_norm_1", None), getattr(b, "post_norm_2", None))]:
             for v in (vars(obj).values() if obj is not None else ()):
                 if isinstance(v, torch.Tensor):
                     add(v)

@@ -285,3 +285,88 @@ class RotaryWindowAttention:
 
     def forward(self, h, residual, ctx, cache, state=None, writes_cache: bool = True):
         return ops.linear(self._inner(h, ctx, cache, writes_cache), self.w_out, None, w_is_nk=True, residual=residual)
+
+
+@register_mixer("latent_attention")
+class LatentAttention:
+    """Attention whose keys and values are made from ONE small latent per token, with a sliding window:
+
+        q = W_q h, per head [head_dim plain | rot_dim rotated]
+        W_dkv h = [kv_rank numbers | rot_dim numbers]: the first part, RMS-normed (weight `dkv_norm`), is the latent c; the second,
+            rotated, is a key part k_rot that all heads share
+        head n: k_plain = W_uk[n] c, v = W_uv[n] c; score = (q_plain . k_plain + q_rot . k_rot) * scale; softmax over the keys
+            (p - window, p] (window 0: all up to p); output W_o [heads' sum_j p_j v_j]
+
+    Rotation: of the rotated parts the first rot_dims dimensions, the pairs (2i, 2i + 1), by the angle position * rot_freqs[i],
+    with cos and sin multiplied by rot_magnitude (the caller makes the frequencies: plain or stretched ones).
+
+    Only [c | k_rot] is cached (one row per token for all heads; a member whose values lie in its key rows). The products with
+    W_uk and W_uv move to the query side: q_lat = W_uk[n]^T q_plain, score = (q_lat . c + q_rot . k_rot) * scale, and
+    v-side W_uv[n] (sum_j p_j c_j), so that every head reads the same cache rows: multi-query attention over rows of
+    kv_rank + rot_dim numbers.
+
+    params: n_heads, head_dim, rot_dim, v_head_dim, kv_rank, scale, window, rot_dims, rot_freqs, rot_magnitude, norm_eps.
+    weights (stored [out, in], no biases): w_q [H (head_dim + rot_dim), D], w_dkv [kv_rank + rot_dim, D], dkv_norm [kv_rank], w_uk
+    [H head_dim, kv_rank], w_uv [H v_head_dim, kv_rank], w_out [D, H v_head_dim]."""
+
+    def __init__(self, params: dict, weights: dict, rt: Runtime):
+        self.n_heads, self.head_dim, self.rot_dim = int(params["n_heads"]), int(params["head_dim"]), int(params["rot_dim"])
+        self.v_head_dim, self.kv_rank = int(params["v_head_dim"]), int(params["kv_rank"])
+        self.scale, self.window, self.norm_eps = float(params["scale"]), int(params.get("window", 0)), float(params["norm_eps"])
+        self.rot_dims, self.rot_magnitude = int(params.get("rot_dims", 0)), float(params.get("rot_magnitude", 1.0))
+        freqs = [float(f) for f in params.get("rot_freqs", ())]
+        if self.rot_dims % 2 or not 0 <= self.rot_dims <= self.rot_dim or len(freqs) != self.rot_dims // 2:
+            raise ValueError(f"latent attention: {self.rot_dims} rotated dimensions of {self.rot_dim} with {len(freqs)} frequencies")
+        self.q_head, self.row = self.head_dim + self.rot_dim, self.kv_rank + self.rot_dim
+        H = self.n_heads
+        shapes = {"w_q": (H * self.q_head, None), "w_dkv": (self.row, None), "dkv_norm": (self.kv_rank,), "w_uk": (H * self.head_dim, self.kv_rank),
+                  "w_uv": (H * self.v_head_dim, self.kv_rank), "w_out": (None, H * self.v_head_dim)}
+        for name, want in shapes.items():
+            have = tuple(weights[name].shape)
+            if len(have) != len(want) or any(w is not None and w != g for w, g in zip(want, have)):
+                raise ValueError(f"latent attention: {name} {have} does not fit {H} heads of {self.head_dim} + {self.rot_dim} "
+                                 f"(values {self.v_head_dim}) over a latent of {self.kv_rank}")
+        if self.row > 256:
+            raise ValueError(f"latent attention: cache rows of {self.row} numbers exceed the kernels' 256")
+        self.w_in = matrix(torch.cat([weights["w_q"], weights["w_dkv"]], dim=0), rt)
+        self.w_uk, self.w_uv = matrix(weights["w_uk"], rt), matrix(weights["w_uv"], rt)
+        self.w_out = matrix(weights["w_out"], rt)
+        self.dkv_norm = vector(weights["dkv_norm"], rt)
+        # frequencies: made in float64 by the caller, rounded once to float32
+        self.freqs = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(rt.device)
+
+    def matrices(self):
+        return [self.w_in, self.w_uk, self.w_uv, self.w_out]
+
+    @property
+    def cache_spec(self) -> MemberSpec:
+        return MemberSpec(1, self.row, self.window, self.kv_rank, 0, values_in_keys=True)
+
+    state_spec = None
+    capturable = True
+
+    def _inner(self, h, ctx, cache, writes_cache):
+        H, d, c = self.n_heads, self.head_dim, self.kv_rank
+        proj = ops.linear(h, self.w_in, None, w_is_nk=True)
+        queries = torch.empty(proj.shape[0], H * self.row, dtype=proj.dtype, device=proj.device)
+        # norm of the latent, both rotations, the cache write and the copy of the rotated query parts: one launch
+        ops.latent_prepare(proj, H, self.q_head, d, self.rot_dim, self.rot_dims, H * self.q_head, c, self.dkv_norm, self.norm_eps,
+                           self.freqs, self.rot_magnitude, ctx.positions,
+                           k_cache=cache.k if writes_cache else None, slot_mapping=ctx.slot_mapping[cache.group],
+                           page_size=cache.page_size, page_stride=cache.page_stride, n_pages=cache.n_pages,
+                           q_out=queries, q_out_head_dim=self.row, q_out_off=c)
+        ops.head_linear(proj, self.q_head, self.w_uk, False, queries, self.row, H, d, c)
+        mixed = ops.paged_attention(
+            queries, cache.k, cache.k, cache.page_stride, cache.page_size, cache.n_pages, ctx.block_tables[cache.group], ctx.row_entry,
+            ctx.positions, ctx.seq_lens, H, 1, self.row, self.scale, self.window, decode_only=ctx.decode_only,
+            max_context=ctx.max_context, q_start=ctx.q_start, n_tiles=ctx.n_attention_tiles, v_head_dim=c, values_in_keys=True)
+        out = torch.empty(proj.shape[0], H * self.v_head_dim, dtype=proj.dtype, device=proj.device)
+        ops.head_linear(mixed, c, self.w_uv, True, out, self.v_head_dim, H, c, self.v_head_dim)
+        return out
+
+    def mix(self, h, ctx, cache=None, state=None, writes_cache: bool = True):
+        """The mixer's output [T, D] in float32, without the residual stream."""
+        return ops.linear(self._inner(h, ctx, cache, writes_cache), self.w_out, None, w_is_nk=True, out_dtype=torch.float32)
+
+    def forward(self, h, residual, ctx, cache, state=None, writes_cache: bool = True):
+        return ops.linear(self._inner(h, ctx, cache, writes_cache), self.w_out, None, w_is_nk=True, residual=residual)

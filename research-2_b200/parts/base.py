@@ -71,6 +71,8 @@ class LayerSpec:
     feed_forward: PartSpec | None  # None: a layer without a feed-forward (arrangements that allow it)
     norm_1: PartSpec
     norm_2: PartSpec | None = None  # None: an arrangement with one norm
+    post_norm_1: PartSpec | None = None  # arrangements with a norm after each sublayer as well
+    post_norm_2: PartSpec | None = None
 
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {

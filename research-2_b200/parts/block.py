@@ -83,3 +83,33 @@ class ParallelBlock:
         if self.feed_forward is not None:
             x = self.feed_forward.forward(h, x, ctx)
         return x
+
+
+@register_block("sandwich")
+class SandwichBlock:
+    """A norm before AND after each sublayer: x + post_1(mixer(norm_1 x)), then x + post_2(feed_forward(norm_2 x)). The
+    sublayers hand over their output in float32 without the stream (`mix`); one launch normalises it, adds it to the stream
+    and, after the mixer, also gives the feed-forward's normed input. The post norms are RMS norms (`gain`, `eps`). A layer
+    may have no feed-forward (None; then no norm_2 and no post_norm_2)."""
+
+    def __init__(self, norm_1, mixer, norm_2, feed_forward, compute_dtype, post_norm_1=None, post_norm_2=None):
+        if post_norm_1 is None or (feed_forward is not None and (norm_2 is None or post_norm_2 is None)):
+            raise ValueError("a sandwich block needs a norm after every sublayer that it has")
+        for part, what in ((mixer, "mixer"), (feed_forward, "feed-forward")):
+            if part is not None and not hasattr(part, "mix"):
+                raise ValueError(f"a sandwich block's {what} must offer `mix` (its output without the stream)")
+        for norm in (post_norm_1, post_norm_2, norm_2):
+            if norm is not None and not hasattr(norm, "gain"):
+                raise ValueError("a sandwich block's norms after the sublayers, and the one between them, must be RMS norms")
+        self.norm_1, self.mixer, self.norm_2, self.feed_forward = norm_1, mixer, norm_2, feed_forward
+        self.post_norm_1, self.post_norm_2 = post_norm_1, post_norm_2
+        self.compute_dtype = compute_dtype
+
+    def forward(self, x, ctx, cache=None, state=None, writes_cache: bool = True):
+        h = self.norm_1.forward(x, self.compute_dtype)
+        y = self.mixer.mix(h, ctx, cache, state, writes_cache)
+        if self.feed_forward is None:
+            return ops.norm_add(x, y, self.post_norm_1.gain, self.post_norm_1.eps)
+        x, h = ops.norm_add(x, y, self.post_norm_1.gain, self.post_norm_1.eps, self.norm_2.gain, self.norm_2.eps, self.compute_dtype)
+        y = self.feed_forward.mix(h, ctx)
+        return ops.norm_add(x, y, self.post_norm_2.gain, self.post_norm_2.eps)

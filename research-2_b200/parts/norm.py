@@ -35,7 +35,8 @@ class LayerNorm:
 class RMSNorm:
     """x / sqrt(mean(x^2) + eps) * gain. params: eps; unit_offset (the stored weight is the gain's offset from one:
     gain = 1 + weight; default false: the weight is the gain); gain_scale (default 1: a constant factor on the normalised
-    rows, folded into the gain, for instance the factor on a model's logits in its last norm). weights: weight."""
+    rows, folded into the gain, for instance the factor on a model's logits in its last norm); width (needed where the stored
+    weight is ONE number, the gain of all coordinates: it is spread over `width` coordinates here). weights: weight."""
 
     can_be_lazy = True
 
@@ -43,6 +44,8 @@ class RMSNorm:
         self.eps = float(params["eps"])
         self.unit_offset = bool(params.get("unit_offset", False))
         weight = vector(weights["weight"], rt)
+        if weight.dim() == 0 or (weight.numel() == 1 and "width" in params):   # one gain for all coordinates
+            weight = weight.reshape(1).expand(int(params["width"])).contiguous()
         self.gain = weight + 1.0 if self.unit_offset else weight   # in float32, as the kernels would add it
         if float(params.get("gain_scale", 1.0)) != 1.0:
             self.gain = self.gain * float(params["gain_scale"])

@@ -1,6 +1,6 @@
 """Mixers that carry a state of fixed size per request instead of a cache that grows with the sequence:
-a matrix memory with exponential gates (mLSTM) and a state-space layer with a short causal convolution
-(the recurrence of Mamba-2). Their state lives in 32-bit floats in the request's state slot, starts at
+a matrix memory with exponential gates (mLSTM), retention (linear attention with a fixed decay per head) and a
+state-space layer with a short causal convolution (the recurrence of Mamba-2). Their state lives in 32-bit floats in the request's state slot, starts at
 zero with a sequence's first token and is carried from step to step; prompts, portions and single decoded
 tokens run through the same kernels (csrc/kernels/recurrent.cu), entry by entry, row by row.
 
@@ -69,6 +69,64 @@ class MatrixMemory:
         o = ops.mlstm_scan(proj[:, :a], proj[:, a:b], proj[:, b: b + self.v_width], gates, self.gate_cap, self.head_dim ** -0.5,
                            state, ctx.q_start, ctx.state_slot, ctx.fresh, self.n_heads, self.head_dim, self.v_head_dim)
         return ops.group_norm_gated(o, proj[:, b + self.v_width:], self.norm, self.n_heads, self.norm_eps, False, proj.dtype)
+
+    def mix(self, h, ctx, cache=None, state=None, writes_cache: bool = True):
+        return ops.linear(self._inner(h, ctx, state), self.w_out, None, w_is_nk=True, out_dtype=torch.float32)
+
+    def forward(self, h, residual, ctx, cache=None, state=None, writes_cache: bool = True):
+        return ops.linear(self._inner(h, ctx, state), self.w_out, None, w_is_nk=True, residual=residual)
+
+
+@register_mixer("retention")
+class Retention:
+    """Linear attention with one fixed decay per head and neither softmax nor denominator. Per head:
+
+        S' = decay S + k v^T   (S: [head_dim x v_head_dim], from zero),   o = S'^T q
+        q = rotate(W_q h), k = rotate(W_k h) head_dim^-1/2, v = W_v h
+
+    (rotation: of each head the first rot_dims dimensions, dimension i with i + rot_dims / 2, by the angle position *
+    rot_freqs[i]). Each head's o is divided by its root mean square (no gain), the heads are concatenated, multiplied by
+    silu(W_g h) and projected by W_o. The rotation happens inside the recurrence's kernel, in float32: what enters the
+    recurrence is the projections' values and nothing rounded after them.
+
+    params: n_heads, head_dim, v_head_dim, decay (one number per head), rot_dims, rot_freqs, norm_eps.
+    weights (stored [out, in], no biases): w_q, w_k [H head_dim, D], w_v, w_gate [H v_head_dim, D], w_out [D, H v_head_dim]."""
+
+    def __init__(self, params: dict, weights: dict, rt: Runtime):
+        self.n_heads, self.head_dim, self.v_head_dim = int(params["n_heads"]), int(params["head_dim"]), int(params["v_head_dim"])
+        self.norm_eps, self.rot_dims = float(params["norm_eps"]), int(params.get("rot_dims", 0))
+        decay, freqs = [float(x) for x in params["decay"]], [float(f) for f in params.get("rot_freqs", ())]
+        if len(decay) != self.n_heads or self.rot_dims % 2 or not 0 <= self.rot_dims <= self.head_dim or len(freqs) != self.rot_dims // 2:
+            raise ValueError(f"retention: {len(decay)} decays for {self.n_heads} heads, {self.rot_dims} rotated dimensions of "
+                             f"{self.head_dim} with {len(freqs)} frequencies")
+        self.qk_width, self.v_width = self.n_heads * self.head_dim, self.n_heads * self.v_head_dim
+        stacked = [weights["w_q"], weights["w_k"], weights["w_v"], weights["w_gate"]]
+        if [w.shape[0] for w in stacked] != [self.qk_width, self.qk_width, self.v_width, self.v_width] or weights["w_out"].shape[1] != self.v_width:
+            raise ValueError(f"retention: projections {[tuple(w.shape) for w in stacked]} and an output of {tuple(weights['w_out'].shape)} "
+                             f"do not fit {self.n_heads} heads of {self.head_dim} x {self.v_head_dim}")
+        self.w_in = matrix(torch.cat(stacked, dim=0), rt)
+        self.w_out = matrix(weights["w_out"], rt)
+        # decays and frequencies: exact in float64, rounded once to float32
+        self.decay = torch.tensor(decay, dtype=torch.float64).to(torch.float32).to(rt.device)
+        self.freqs = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(rt.device)
+
+    cache_spec = None
+    capturable = True
+
+    def matrices(self):
+        return [self.w_in, self.w_out]
+
+    @property
+    def state_spec(self) -> StateSpec:
+        return StateSpec((self.n_heads * self.head_dim * self.v_head_dim,), torch.float32)
+
+    def _inner(self, h, ctx, state):
+        proj = ops.linear(h, self.w_in, None, w_is_nk=True)
+        a, b = self.qk_width, 2 * self.qk_width
+        o = ops.retention_scan(proj[:, :a], proj[:, a:b], proj[:, b: b + self.v_width], self.decay, self.head_dim ** -0.5, self.freqs,
+                               self.rot_dims, ctx.positions, state, ctx.q_start, ctx.state_slot, ctx.fresh, self.n_heads, self.head_dim,
+                               self.v_head_dim)
+        return ops.group_norm_gated(o, proj[:, b + self.v_width:], None, self.n_heads, self.norm_eps, "silu_after", proj.dtype)
 
     def mix(self, h, ctx, cache=None, state=None, writes_cache: bool = True):
         return ops.linear(self._inner(h, ctx, state), self.w_out, None, w_is_nk=True, out_dtype=torch.float32)
