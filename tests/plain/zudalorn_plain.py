@@ -23,9 +23,18 @@ def unit_rms(x, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
 
-def scalar_norm(x, g, eps):
+# A test may set this to a function that disturbs every normalised row on its way into a sublayer (and into the head):
+# how far the logits of a position move under small disturbances says how well-conditioned the position is.
+DISTURB = None
+# A test may set this to a list: every router then appends, per position, how narrowly its choice was made (the smallest
+# gap between something chosen and something not, among experts and among groups).
+MARGINS = None
+
+
+def scalar_norm(x, g, eps, entering=False):
     """RMS norm whose gain is ONE number for all coordinates."""
-    return unit_rms(x, eps) * float(g)
+    out = unit_rms(x, eps) * float(g)
+    return DISTURB(out) if (entering and DISTURB is not None) else out
 
 
 # ---- rotations ---------------------------------------------------------------------------------
@@ -152,20 +161,27 @@ def route(z, correction, top, n_groups, keep):
     T, E = z.shape
     s = torch.sigmoid(z)
     choice = s + correction.to(F64)
-    chosen, weights = [], []
+    chosen, weights, margins = [], [], []
     size = E // n_groups
     for t in range(T):
         c = choice[t].clone()
-        if n_groups > 1 or keep < n_groups:
+        margin = math.inf
+        if keep < n_groups:
             marks = [float(torch.topk(c[g * size: (g + 1) * size], min(2, size)).values.sum()) for g in range(n_groups)]
-            best = sorted(range(n_groups), key=lambda g: (-marks[g], g))[:keep]
-            for g in range(n_groups):
-                if g not in best:
-                    c[g * size: (g + 1) * size] = -math.inf
-        order = sorted(range(E), key=lambda e: (-float(c[e]), e))[:top]
+            ranked = sorted(range(n_groups), key=lambda g: (-marks[g], g))
+            margin = marks[ranked[keep - 1]] - marks[ranked[keep]]
+            for g in ranked[keep:]:
+                c[g * size: (g + 1) * size] = -math.inf
+        ranked = sorted(range(E), key=lambda e: (-float(c[e]), e))
+        order = ranked[:top]
+        if top < E and float(c[ranked[top]]) > -math.inf:
+            margin = min(margin, float(c[ranked[top - 1]] - c[ranked[top]]))
+        margins.append(margin)
         sel = s[t][order]
         chosen.append(order)
         weights.append(sel / (sel.sum() + 1e-20))
+    if MARGINS is not None:
+        MARGINS.append(torch.tensor(margins, dtype=F64))
     return chosen, weights
 
 
@@ -190,13 +206,32 @@ def forward(config, w, tokens, layers_out=None):
     x = w["embed"].to(F64)[torch.tensor(tokens)]
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
-        h = scalar_norm(x, w[p + "norm1"], eps)
+        h = scalar_norm(x, w[p + "norm1"], eps, entering=True)
         mixer = latent_attention if layer["type"] == "latent_attention" else retention
         x = x + scalar_norm(mixer(h, w, p + "mix.", layer["mixer"], eps), w[p + "norm1b"], eps)
         if layer.get("mlp") is not None:
-            h = scalar_norm(x, w[p + "norm2"], eps)
+            h = scalar_norm(x, w[p + "norm2"], eps, entering=True)
             y = dense(h, w, p + "mlp.") if layer["mlp"]["kind"] == "dense" else experts(h, w, p + "mlp.", layer["mlp"])
             x = x + scalar_norm(y, w[p + "norm2b"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
-    return lin(w["head"], scalar_norm(x, w["final.norm"], eps))
+    return lin(w["head"], scalar_norm(x, w["final.norm"], eps, entering=True))
+
+
+def read_model(folder):
+    """(config.json as a dict, tensors by name in float64)."""
+    import json
+    from pathlib import Path
+
+    from safetensors.torch import load_file
+
+    folder = Path(folder)
+    return json.loads((folder / "config.json").read_text()), {n: t.to(F64) for n, t in load_file(str(folder / "model.safetensors")).items()}
+
+
+def generate(config: dict, w: dict, prompt: list[int], n_new: int) -> list[int]:
+    """Greedy continuation, recomputing the whole sequence for every token (first index on ties)."""
+    seq = list(prompt)
+    for _ in range(n_new):
+        seq.append(int(forward(config, w, seq)[-1].argmax()))
+    return seq[len(prompt):]
