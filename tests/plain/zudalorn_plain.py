@@ -85,8 +85,10 @@ def latent_attention(h, w, p, cfg, eps):
     token, plus ONE rotated key part per token that all heads share. Sliding window, ordinary softmax."""
     T = h.shape[0]
     H, d, r, dv, c_dim = cfg["heads"], cfg["dim"], cfg["rot_dim"], cfg["vdim"], cfg["kv_rank"]
-    rot = cfg["rot"]
-    if rot.get("scaling"):
+    rot = cfg.get("rot")
+    if not rot:
+        freqs, mag = [], 1.0
+    elif rot.get("scaling"):
         freqs, mag = yarn_frequencies(rot["dims"], rot["base"], rot["scaling"])
     else:
         freqs, mag = plain_frequencies(rot["dims"], rot["base"]), 1.0
