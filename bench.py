@@ -20,7 +20,7 @@ A "step" is one decode step. The default run decodes a batch of 8 requests whose
   kernels    the step's dominant kernels one by one: microseconds and fraction of the measured peak
 
 `--design bosenex` prints the same points for a Bosenex model beside a Zirunex model of equal layer sizes, and the
-design's kernels one by one. `--design zirunex` prints, instead, the same decode and prefill points for Zirunex models with the layer sizes
+design's kernels one by one; `--design zudalorn` a Zudalorn model beside a Bosenex model of equal layer sizes, likewise. `--design zirunex` prints, instead, the same decode and prefill points for Zirunex models with the layer sizes
 of `--model` beside GPT-2's, and the design's kernels one by one beside their likes.
 
 `--model gpt2-355M` and `--model gpt2-1.5B` run the same at those sizes (the 1.5B decode workload has
@@ -281,6 +281,8 @@ def prefill_point(model, cfg, pk: dict) -> dict:
         flops = 2 * t * layers * (3 * d * d + d * d + 2 * d * f) + layers * n_req * 4 * d * length * (length + 1) / 2 + 2 * n_req * d * v
     elif hasattr(cfg, "logit_scale"):
         flops = bosenex_flops(cfg, n_req, length)
+    elif type(cfg).__name__ == "ZudalornConfig":
+        flops = zudalorn_flops(cfg, n_req, length)
     else:
         flops = gated_design_flops(cfg, n_req, length)
     return {"value": t / (ms / 1e3), "tokens": t, "ms": ms, "frac": flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
@@ -383,6 +385,11 @@ def design_points(args, pk: dict) -> dict:
     return out
 
 
+def kv_heads_for(h: int) -> int:
+    """About four query heads a key/value head: the largest divisor of h up to h / 4."""
+    return max(k for k in range(1, max(1, h // 4) + 1) if h % k == 0)
+
+
 def bosenex_config(size: str, n_layer: int) -> dict:
     """A Bosenex configuration with the width, heads, head size, layers and vocabulary of a GPT-2 size: of every three
     layers two are matrix memories (query/key heads half as wide as value heads) and one is attention (4 query heads a
@@ -394,7 +401,7 @@ def bosenex_config(size: str, n_layer: int) -> dict:
     hd = d // h
     ff = max(128, round(2 * g["n_inner"] / 3 / 128) * 128)
     memory = {"heads": h, "dim": hd // 2, "vdim": hd, "gate_cap": 15.0}
-    pair = {"left": {"heads": h, "kv_heads": max(1, h // 4), "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0,
+    pair = {"left": {"heads": h, "kv_heads": kv_heads_for(h), "dim": hd, "vdim": hd, "scale": hd ** -0.5, "softcap": 30.0,
                      "mask": {"size": 256}, "rot": {"dims": hd, "base": 10000.0}},
             "right": {"heads": 2 * h, "vdim": hd, "state": 64, "groups": 1, "conv": 4, "norm_groups": 1}}
     moe = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 4, "limit": 7.0}, "shared": {"ff": ff // 4, "limit": 7.0}}
@@ -537,6 +544,199 @@ def bosenex_points(args, pk: dict) -> dict:
             n_bytes=t * gu.shape[1] * 3)
         gu_like = torch.randn(t, 2 * ff, device=dev).to(bf)
         add(f"its like: gated unit of {ff:,} columns (Zirunex), {label}", lambda: ops.gated_act(gu_like, 7.0, 1.702, 1.0), n_bytes=t * ff * 6)
+    out["kernels"] = table
+    return out
+
+
+def zudalorn_config(size: str, n_layer: int) -> dict:
+    """A Zudalorn configuration with the width, heads, head size, layers and vocabulary of a GPT-2 size, laid out like the
+    Bosenex configuration beside it: of every three layers two are retention (query/key heads half as wide as value heads,
+    fully rotated) and one is latent attention (per head a plain part of the head size and a rotated part of half of it, a
+    latent of two head sizes, window 256, stretched rotation). The first layer's feed-forward is dense: two matrices where
+    a gated one has three, so its inner width is 3/2 of the gated width beside it; the others route each token to 2 of 8
+    experts (4 groups of which 2 are kept) of a quarter of the gated width and add one gated expert for every token."""
+    g = SIZES[size]
+    d, h = g["n_embd"], g["n_head"]
+    hd = d // h
+    ff = max(128, round(2 * g["n_inner"] / 3 / 128) * 128)
+    retention = {"heads": h, "dim": hd // 2, "vdim": hd, "decay": [1.0 - 2.0 ** (-5.0 - 3.0 * i / max(1, h - 1)) for i in range(h)],
+                 "rot": {"dims": hd // 2, "base": 10000.0}}
+    latent = {"heads": h, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 2 * hd, "scale": (hd + hd // 2) ** -0.5, "mask": {"size": 256},
+              "rot": {"dims": hd // 2, "base": 10000.0, "scaling": {"factor": 4.0, "original": 256, "fast": 32.0, "slow": 1.0}}}
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}, "expert": {"ff": ff // 4}, "shared": {"ff": ff // 4}}
+    layers = [{"type": "latent_attention" if i % 3 == 2 else "retention", "mixer": latent if i % 3 == 2 else retention,
+               "mlp": {"kind": "dense", "ff": 3 * ff // 2} if i == 0 else moe} for i in range(n_layer)]
+    return {"architecture": "Zudalorn", "vocab": g["vocab_size"], "width": d, "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def zudalorn_flops(cfg, n_req: int, length: int) -> float:
+    """Flops that one prefill step of n_req prompts of `length` tokens NEEDS in a Zudalorn configuration: products with the
+    weights a token uses (its chosen experts, not all), the recurrences, and the attention's seen pairs over latent rows
+    (the keys' and values' small matrices applied on the query side, once per row and head)."""
+    from research_2_b200.config.zudalorn import DenseMlp, LatentAttentionMixer
+
+    t, d, total = n_req * length, cfg.width, 0.0
+    for layer in cfg.layers:
+        m = layer.mixer
+        if isinstance(m, LatentAttentionMixer):
+            row = m.kv_rank + m.rot_dim
+            total += 2 * t * d * (m.heads * (m.dim + m.rot_dim) + row) + 2 * t * m.heads * m.vdim * d
+            total += 2 * t * m.heads * m.kv_rank * (m.dim + m.vdim)
+            total += n_req * 2 * m.heads * (row + m.kv_rank) * sum(min(i + 1, m.window or length) for i in range(length))
+        else:
+            qk, v = m.heads * m.dim, m.heads * m.vdim
+            total += 2 * t * d * (2 * qk + 2 * v) + 2 * t * v * d + t * m.heads * 6 * m.dim * m.vdim
+        if isinstance(layer.mlp, DenseMlp):
+            total += 2 * t * d * 2 * layer.mlp.ff
+        elif layer.mlp is not None:
+            total += 2 * t * d * 3 * (layer.mlp.top * layer.mlp.ff + layer.mlp.shared_ff)
+    return total + 2 * n_req * d * cfg.vocab_size
+
+
+def zudalorn_points(args, pk: dict) -> dict:
+    """`--design zudalorn`: prefill and decode throughput of a Zudalorn model with the layer sizes of `--model`, beside a
+    Bosenex model of that size (the closest of the other models: two recurrent layers to one of windowed attention,
+    routed experts with one for every token) through the same loops, and the design's kernels one by one beside their likes."""
+    import torch
+    from research_2_b200.kernels import ops
+    from research_2_b200.profiling import kernel_cases
+
+    g = SIZES[args.model]
+    d, h = g["n_embd"], g["n_head"]
+    hd = d // h
+    variants = {"bosenex": bosenex_config(args.model, args.layers), "zudalorn": zudalorn_config(args.model, args.layers)}
+    out = {"design": "zudalorn", "sizes_of": args.model, "layers": args.layers, "prompt_len": PROMPT_LEN, "models": {}}
+    for name, data in variants.items():
+        model, cfg = build_gated_design(data)
+        point = {}
+        for batch in (8, 64):
+            steps = min(args.steps, 96)
+            value, ms, loop, kv_bytes = decode_point(model, batch, steps, args.warmup)
+            state_bytes = 2 * batch * sum(4 * int(torch.tensor(spec.shape).prod()) for spec in model.state_members)   # read and written
+            achieved = (model.weight_bytes_per_step() + kv_bytes + state_bytes) / (ms / 1e3) / 1e9
+            point[f"decode_b{batch}"] = {"tokens/s": round(value), "ms_per_step": round(ms, 4), "kernels_per_step": loop.graph.kernels,
+                                         "hbm_frac": round(achieved / pk["hbm_gbs"], 3)}
+            del loop
+            torch.cuda.empty_cache()
+        pre = prefill_point(model, cfg, pk)
+        point["prefill_2x1024"] = {"tokens/s": round(pre["value"]), "ms": round(pre["ms"], 3), "bf16_frac": round(pre["frac"], 3)}
+        out["models"][name] = point
+        del model
+        torch.cuda.empty_cache()
+
+    # the design's kernels one by one, at a prompt step (2 x 1,024 rows) and a decode step (8 rows at position 1,023)
+    table = {}
+
+    def add(name, fn, n_bytes=0, flops=0):
+        us = kernel_cases.time_in_graph(fn)
+        entry = {"us": round(us, 2)}
+        if n_bytes:
+            entry.update(frac=round(n_bytes / us / 1e3 / pk["hbm_gbs"], 3), of="copy bandwidth")
+        if flops:
+            entry.update(flops_frac=round(flops / us / 1e6 / pk["bf16_tflops"], 4))
+        table[name] = entry
+
+    dev, bf = "cuda:0", torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)  # noqa: E731
+    ff = max(128, round(2 * g["n_inner"] / 3 / 128) * 128)
+    page, window, length = PAGE, 256, 1024
+    for label, n_entries, rows_each in (("2 x 1,024 rows", 2, 1024), ("8 decoded rows", 8, 1)):
+        t = n_entries * rows_each
+        q_start = i32([i * rows_each for i in range(n_entries + 1)])
+        slots, fresh = i32(list(range(n_entries))), i32([0] * n_entries)
+        row_entry = i32([e for e in range(n_entries) for _ in range(rows_each)])
+        positions = i32([length - 1 if rows_each == 1 else p for _ in range(n_entries) for p in range(rows_each)])
+        seq_lens = i32([length] * n_entries)
+        n_tiles = n_entries * -(-rows_each // 64)
+        pages_each = length // page
+        tables = torch.arange(n_entries * pages_each, dtype=torch.int32, device=dev).view(n_entries, pages_each).contiguous()
+        seen = sum(min(p + 1, window) for p in positions.tolist())   # (row, key) pairs inside the windows
+        keys_read = n_entries * (length if rows_each > 1 else window)  # distinct cache rows that the step reads
+        x32, y32 = torch.randn(t, d, device=dev), torch.randn(t, d, device=dev)
+        hrow = torch.randn(t, d, device=dev).to(bf)
+        gain = torch.ones(d, device=dev)
+        add(f"a sublayer's output normed into the stream + the next norm, {label}", lambda: ops.norm_add(x32, y32, gain, 1e-5, gain, 1e-5, bf),
+            n_bytes=t * d * 14)
+        add(f"its like: two mixers join the stream (Bosenex), {label}", lambda: ops.pair_norm_add(x32, y32, y32, gain, gain, 1e-5), n_bytes=t * d * 16)
+        # latent attention: the launch between the input product and the attention kernel, the small products per head, the attention
+        c, r = 2 * hd, hd // 2
+        row, q_head = c + r, hd + r
+        proj = torch.randn(t, h * q_head + row, device=dev).to(bf)
+        queries = torch.randn(t, h * row, device=dev).to(bf)
+        lat_cache = torch.randn(n_entries * pages_each, page * row, device=dev).to(bf)
+        slot_map = i32([e * length + p for e, p in zip(row_entry.tolist(), positions.tolist())])
+        norm_w = torch.ones(c, device=dev)
+        freq = torch.tensor([10000.0 ** (-2.0 * i / r) for i in range(r // 2)], device=dev)
+        add(f"latent attention: latent's norm, rotations, cache row, {label}",
+            lambda: ops.latent_prepare(proj, h, q_head, hd, r, r, h * q_head, c, norm_w, 1e-5, freq, 1.1, positions, k_cache=lat_cache.view(-1),
+                                       slot_mapping=slot_map, page_size=page, page_stride=page * row, n_pages=lat_cache.shape[0], q_out=queries,
+                                       q_out_head_dim=row, q_out_off=c), n_bytes=t * (h * r * 6 + row * 6))
+        w_uk = torch.randn(h * hd, c, device=dev).to(bf)
+        add(f"latent attention: keys' matrices onto the queries, {h} heads of {hd} -> {c}, {label}",
+            lambda: ops.head_linear(proj, q_head, w_uk, False, queries, row, h, hd, c), n_bytes=t * h * (hd + c) * 2 + w_uk.numel() * 2,
+            flops=2 * t * h * hd * c)
+        mixed = torch.empty(t, h * c, device=dev, dtype=bf)
+        add(f"latent attention over rows of {row}, {h} heads, window {window}, {label}",
+            lambda: ops.paged_attention(queries, lat_cache.view(-1), lat_cache.view(-1), page * row, page, lat_cache.shape[0], tables, row_entry,
+                                        positions, seq_lens, h, 1, row, 0.1, window, out=mixed, decode_only=rows_each == 1, max_context=length,
+                                        q_start=q_start, n_tiles=n_tiles, v_head_dim=c, values_in_keys=True),
+            n_bytes=t * h * (row + c) * 2 + keys_read * row * 2, flops=2 * seen * h * (row + c))
+        kvh = kv_heads_for(h)
+        qkv = torch.randn(t, (h + 2 * kvh) * hd, device=dev).to(bf)
+        kv_pool = torch.randn(n_entries * pages_each, 2 * kvh * page * hd, device=dev).to(bf).view(-1)
+        att_out = torch.empty(t, h * hd, device=dev, dtype=bf)
+        add(f"its like: attention, {h} heads of {hd} over {kvh} kv heads, window {window}, capped scores (Bosenex), {label}",
+            lambda: ops.paged_attention(qkv[:, : h * hd], kv_pool, kv_pool[kvh * page * hd:], 2 * kvh * page * hd, page, n_entries * pages_each, tables,
+                                        row_entry, positions, seq_lens, h, kvh, hd, hd ** -0.5, window, out=att_out, decode_only=rows_each == 1,
+                                        max_context=length, q_start=q_start, n_tiles=n_tiles, softcap=30.0),
+            n_bytes=t * h * hd * 4 + keys_read * 2 * kvh * hd * 2, flops=2 * seen * h * 2 * hd)
+        w_uv = torch.randn(h * hd, c, device=dev).to(bf)
+        heads_out = torch.empty(t, h * hd, device=dev, dtype=bf)
+        add(f"latent attention: values' matrices after the sums, {h} heads of {c} -> {hd}, {label}",
+            lambda: ops.head_linear(mixed, c, w_uv, True, heads_out, hd, h, c, hd), n_bytes=t * h * (hd + c) * 2 + w_uv.numel() * 2,
+            flops=2 * t * h * hd * c)
+        inv_freq = torch.tensor([10000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], device=dev)
+        add(f"its like: rotation of {h + kvh} heads of {hd} (Bosenex), {label}", lambda: ops.rotate_half(qkv, h + kvh, hd, hd, inv_freq, positions),
+            n_bytes=t * (h + kvh) * hd * 4)
+        # retention beside the matrix memory
+        dk = hd // 2
+        rproj = torch.randn(t, 2 * h * dk + 2 * d, device=dev).to(bf)
+        decay = torch.full((h,), 0.97, device=dev)
+        rfreq = torch.tensor([10000.0 ** (-2.0 * i / dk) for i in range(dk // 2)], device=dev)
+        rstate = torch.zeros(n_entries, h * dk * hd, device=dev)
+        scan_bytes = t * (2 * h * dk + d) * 2 + t * d * 4 + 2 * rstate.numel() * 4
+        add(f"retention: recurrence with rotation, {h} heads of {dk} x {hd}, {label}",
+            lambda: ops.retention_scan(rproj[:, : h * dk], rproj[:, h * dk: 2 * h * dk], rproj[:, 2 * h * dk: 2 * h * dk + d], decay, dk ** -0.5, rfreq, dk,
+                                       positions, rstate, q_start, slots, fresh, h, dk, hd), n_bytes=scan_bytes)
+        gates = torch.randn(t, 2 * h, device=dev)
+        mstate = torch.zeros(n_entries, h * ops.mlstm_state_floats(dk, hd), device=dev)
+        add(f"its like: matrix memory's recurrence, {h} heads of {dk} x {hd} (Bosenex), {label}",
+            lambda: ops.mlstm_scan(rproj[:, : h * dk], rproj[:, h * dk: 2 * h * dk], rproj[:, 2 * h * dk: 2 * h * dk + d], gates, 15.0, dk ** -0.5,
+                                   mstate, q_start, slots, fresh, h, dk, hd), n_bytes=scan_bytes + 2 * (mstate.numel() - rstate.numel()) * 4)
+        o32 = torch.randn(t, d, device=dev)
+        add(f"retention: heads' norm times silu of the gate, {label}",
+            lambda: ops.group_norm_gated(o32, rproj[:, 2 * h * dk + d:], None, h, 1e-5, "silu_after", bf), n_bytes=t * d * 8)
+        add(f"its like: heads' norm and sigmoid gate (Bosenex), {label}", lambda: ops.group_norm_gated(o32, rproj[:, 2 * h * dk + d:], gain, h, 1e-5, False, bf),
+            n_bytes=t * d * 8)
+        # feed-forwards
+        up = torch.randn(t, 3 * ff // 2, device=dev).to(bf)
+        add(f"dense feed-forward: xIELU of {3 * ff // 2:,} columns, {label}", lambda: ops.xielu(up, 0.7, 0.9), n_bytes=t * up.shape[1] * 4)
+        gu_like = torch.randn(t, 2 * ff, device=dev).to(bf)
+        add(f"its like: gated unit of {ff:,} columns (Bosenex), {label}", lambda: ops.gated_act(gu_like, 7.0, 1.702, 1.0), n_bytes=t * ff * 6)
+        router = torch.randn(9, d, device=dev) * 0.02
+        correction = torch.randn(8, device=dev) * 0.1
+        add(f"router: 8 sigmoid scores + the shared expert's gate in 32-bit, 2 of 4 groups, top 2, {label}",
+            lambda: ops.route_scored(hrow, router, correction, 2, 4, 2, n_extra=1), n_bytes=t * d * 2)
+        router8 = torch.randn(8, d, device=dev) * 0.02
+        add(f"its like: router with 8 logits, top 2, softmax (Bosenex), {label}", lambda: ops.route_top_k(hrow, router8, None, 2), n_bytes=t * d * 2)
+        route, _, _, sg = ops.route_scored(hrow, router, correction, 2, 4, 2, n_extra=1)
+        gu = torch.randn(t, 2 * (8 * (ff // 4) + ff // 4), device=dev).to(bf)
+        add(f"experts' gated silu unit with routing weights and the shared gate, {gu.shape[1] // 2:,} columns, {label}",
+            lambda: ops.expert_act(gu, "silu", route=route, n_experts=8, expert_width=ff // 4, tail_gate=sg), n_bytes=t * gu.shape[1] * 3)
+        route2, _, _ = ops.route_top_k(hrow, router8, None, 2)
+        add(f"its like: experts' clamped unit with routing weights (Bosenex), {gu.shape[1] // 2:,} columns, {label}",
+            lambda: ops.expert_act(gu, "clamped_swish", 7.0, 1.702, 1.0, route=route2, n_experts=8, expert_width=ff // 4, tail_limit=7.0),
+            n_bytes=t * gu.shape[1] * 3)
     out["kernels"] = table
     return out
 
@@ -714,7 +914,7 @@ def main() -> int:
     ap.add_argument("--phases", action="store_true", help="print where a layer's time goes inside the resident decode kernel at --batch rows, and stop")
     ap.add_argument("--logits-ctas", action="store_true", help="print when each CTA of a decode step's logits product starts and ends (its waves), and stop")
     ap.add_argument("--prefill", action="store_true", help="print the prefill point (2 x 1,024 tokens in one step) alone, and stop")
-    ap.add_argument("--design", default=None, choices=("zirunex", "bosenex"),
+    ap.add_argument("--design", default=None, choices=("zirunex", "bosenex", "zudalorn"),
                     help="print prefill and decode throughput of that design at the layer sizes of --model beside GPT-2's, "
                          "and its kernels beside their likes, and stop (the default workload is GPT-2's)")
     args = ap.parse_args()
@@ -749,7 +949,8 @@ def main() -> int:
 
     pk, pk_source = peaks()
     if args.design:
-        print(json.dumps(bosenex_points(args, pk) if args.design == "bosenex" else design_points(args, pk)))
+        points = {"bosenex": bosenex_points, "zudalorn": zudalorn_points}.get(args.design, design_points)
+        print(json.dumps(points(args, pk)))
         return 0
     model, cfg = build_model(args.layers, size=args.model)
     if args.phases:

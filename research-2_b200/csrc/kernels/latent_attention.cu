@@ -14,9 +14,14 @@
 //                       lie side by side in the rows of a and out (with strides of their own) and W holds the heads' matrices
 //                       one after the other. It is what moves the keys' up-projection onto the queries and applies the
 //                       values' up-projection to the heads' weighted sums of latents.
+//   r2_latent_attention the attention proper for bfloat16 on the warp-level tensor cores: a CTA's rows are (token, head) pairs
+//                       of one entry, so that one tile of cache rows serves all heads of several tokens.
+#include <limits.h>
 #include <math.h>
 
 #include "common.cuh"
+#include "mma_sync.cuh"
+#include "sm100_ptx.cuh"
 
 namespace {
 
@@ -133,6 +138,253 @@ latent_prepare_kernel(T* __restrict__ buf, int row_stride, int n_heads, int q_he
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The attention proper on the warp-level tensor cores (bfloat16 in, float scores, weights and sums).
+//
+// Every head reads the same cache rows, so a CTA's 64 rows of the first product are (token, head) pairs of one entry:
+// tokens_here consecutive tokens x heads_here heads, 16 pairs to a warp. A portion of a prompt fills the 64 rows with a
+// few tokens and all their heads; a single decoded token fills them with its heads alone. Key rows come in tiles of 64
+// through two buffers (16-byte asynchronous copies through the block table; element by element where a row's length or
+// an address is no multiple of 16 bytes), rows padded with zeros to a multiple of 16 numbers. A key's value is the
+// first kv_rank numbers of its row: the second product reads the same tile, transposed by ldmatrix. Scores are scaled and
+// masked in float (causal, window, context length), the softmax is online, and its weights enter the second product
+// rounded to bfloat16, or with `split_p` as the sum of two bfloat16 numbers. VT: 16-wide column tiles of the output.
+constexpr int LA_WARPS = 4, LA_ROWS = 64, LA_KEYS = 64;
+
+struct LatentAttnParams {
+  const bf16* q; int q_stride;
+  bf16* out; int out_stride;
+  const bf16* cache; long long page_stride; int page_size, page_shift, n_pages;
+  const int32_t* block_tables; int table_width;
+  const int32_t* q_start; const int32_t* positions; const int32_t* seq_lens; int n_entries;
+  int n_heads, heads_here, tokens_here;
+  int row, kv_rank, row_pad;
+  float scale; int window; int split_p;
+  int q_vec, k_vec, out_vec;   // 16-byte loads of queries / of cache rows, 4-byte stores of outputs are possible
+};
+
+// eight numbers of a row from column c * 8 on, zeros from `row` on
+__device__ __forceinline__ uint4 eight_of(const bf16* src_row, int c, int row, bool vec) {
+  if (vec && c * 8 + 8 <= row) return *reinterpret_cast<const uint4*>(src_row + c * 8);
+  __align__(16) bf16 tmp[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) tmp[i] = c * 8 + i < row ? src_row[c * 8 + i] : from_float<bf16>(0.f);
+  return *reinterpret_cast<const uint4*>(tmp);
+}
+
+template <int VT>
+__global__ void __launch_bounds__(LA_WARPS * 32)
+latent_attention_kernel(const LatentAttnParams p) {
+  using namespace r2ptx;
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) uint8_t la_smem[];
+  __shared__ int tile_info[2];
+  const int rs = p.row_pad * 2 + 16;   // bytes of a padded row in shared memory
+  uint8_t* q_s = la_smem;
+  uint8_t* k_s = la_smem + LA_ROWS * rs;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {   // which entry, and which of its tiles, this CTA has
+    int left = blockIdx.x, found = -1, first = 0;
+    for (int e = 0; e < p.n_entries; ++e) {
+      const int n = p.q_start[e + 1] - p.q_start[e];
+      const int tiles = (n + p.tokens_here - 1) / p.tokens_here;
+      if (left < tiles) { found = e; first = p.q_start[e] + left * p.tokens_here; break; }
+      left -= tiles;
+    }
+    tile_info[0] = found;
+    tile_info[1] = first;
+  }
+  __syncthreads();
+  const int e = tile_info[0];
+  if (e < 0) return;
+  const int t0 = tile_info[1];
+  const int n_tok = min(p.tokens_here, p.q_start[e + 1] - t0);
+  const int h0 = blockIdx.y * p.heads_here;
+  const int n_heads_here = min(p.heads_here, p.n_heads - h0);
+  const int seq_len = p.seq_lens[e];
+  const int p_first = p.positions[t0], p_last = p.positions[t0 + n_tok - 1];
+  const int hi = min(p_last, seq_len - 1);                              // newest key that any row sees
+  const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;     // oldest
+  const int n_tiles = hi >= lo ? (hi - lo) / LA_KEYS + 1 : 0;
+  const int32_t* table = p.block_tables + size_t(e) * p.table_width;
+  const int chunks = p.row_pad / 8;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+
+  for (int idx = tid; idx < LA_ROWS * chunks; idx += LA_WARPS * 32) {
+    const int m = idx / chunks, c = idx - m * chunks;
+    const int tok = m / p.heads_here, hh = m - tok * p.heads_here;
+    uint4 v = zero4;
+    if (tok < n_tok && hh < n_heads_here)
+      v = eight_of(p.q + size_t(t0 + tok) * p.q_stride + size_t(h0 + hh) * p.row, c, p.row, p.q_vec != 0);
+    *reinterpret_cast<uint4*>(q_s + m * rs + c * 16) = v;
+  }
+  auto load_keys = [&](int it, int buf) {
+    const int j0 = lo + it * LA_KEYS;
+    uint8_t* tile = k_s + buf * (LA_KEYS * rs);
+    for (int idx = tid; idx < LA_KEYS * chunks; idx += LA_WARPS * 32) {
+      const int key = idx / chunks, c = idx - key * chunks;
+      const int j = j0 + key;
+      uint8_t* dst = tile + key * rs + c * 16;
+      if (j <= hi) {
+        int page = table[page_index(j, p.page_size, p.page_shift)];
+        page = (page < 0 || page >= p.n_pages) ? 0 : page;
+        const bf16* src = p.cache + size_t(page) * p.page_stride + size_t(page_offset(j, p.page_size, p.page_shift)) * p.row;
+        if (p.k_vec && c * 8 + 8 <= p.row) cp_async16(smem_u32(dst), src + c * 8, true);
+        else *reinterpret_cast<uint4*>(dst) = eight_of(src, c, p.row, false);
+      } else {
+        *reinterpret_cast<uint4*>(dst) = zero4;   // no row sees it: zeros, whatever the cache holds there
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  // this thread's two rows of a 16-row piece: g and g + 8; of every 8 columns it has 2 tq and 2 tq + 1
+  const int g = lane >> 2, tq = lane & 3;
+  int pos_r[2], tok_r[2], head_r[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int m = warp * 16 + g + 8 * r;
+    tok_r[r] = m / p.heads_here;
+    head_r[r] = m - tok_r[r] * p.heads_here;
+    const bool valid = tok_r[r] < n_tok && head_r[r] < n_heads_here;
+    pos_r[r] = valid ? min(p.positions[t0 + tok_r[r]], seq_len - 1) : -1;
+    if (!valid) tok_r[r] = -1;
+  }
+  // the positions that this warp's rows span (none: the warp only helps to copy)
+  const int w_tok_first = (warp * 16) / p.heads_here, w_tok_last = min((warp * 16 + 15) / p.heads_here, n_tok - 1);
+  const bool warp_has_rows = w_tok_first < n_tok;
+  const int w_pmin = warp_has_rows ? p.positions[t0 + w_tok_first] : 0, w_pmax = warp_has_rows ? p.positions[t0 + w_tok_last] : -1;
+
+  float o[2 * VT][4];
+#pragma unroll
+  for (int i = 0; i < 2 * VT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  const float scale2 = p.scale * 1.4426950408889634f;   // scores in units of log2(e): one exp2 per weight
+  const int k_steps = p.row_pad / 16;
+
+  if (n_tiles > 0) load_keys(0, 0);
+  for (int it = 0; it < n_tiles; ++it) {
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();   // tile `it` (and, the first time, the queries) is there; nobody reads the other buffer any more
+    if (it + 1 < n_tiles) load_keys(it + 1, (it + 1) & 1);
+    const int j0 = lo + it * LA_KEYS;
+    if (!warp_has_rows || j0 > w_pmax || (p.window > 0 && j0 + LA_KEYS - 1 <= w_pmin - p.window)) continue;
+    const uint32_t kt = smem_u32(k_s) + uint32_t((it & 1) * (LA_KEYS * rs));
+    float s[LA_KEYS / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < LA_KEYS / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll 2
+    for (int ks = 0; ks < k_steps; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldmatrix_x4(smem_u32(q_s) + uint32_t((warp * 16 + (lane & 15)) * rs + (ks * 16 + 8 * (lane >> 4)) * 2), a0, a1, a2, a3);
+#pragma unroll
+      for (int np = 0; np < LA_KEYS / 16; ++np) {   // two 8-key tiles per ldmatrix
+        uint32_t b0, b1, b2, b3;
+        const int key = np * 16 + (lane & 7) + 8 * (lane >> 4);
+        ldmatrix_x4(kt + uint32_t(key * rs + (ks * 2 + ((lane >> 3) & 1)) * 16), b0, b1, b2, b3);
+        mma_bf16(s[2 * np], a0, a1, a2, a3, b0, b1);
+        mma_bf16(s[2 * np + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+    // scale and mask: key k of the tile is seen by a row if lo_r <= k <= hi_r
+    const int hi_a = pos_r[0] - j0, hi_b = pos_r[1] - j0;
+    const int lo_a = p.window > 0 ? pos_r[0] - p.window + 1 - j0 : INT_MIN, lo_b = p.window > 0 ? pos_r[1] - p.window + 1 - j0 : INT_MIN;
+    float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < LA_KEYS / 8; ++nt) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int k = nt * 8 + 2 * tq + c;
+        const bool va = (k <= hi_a) & (k >= lo_a), vb = (k <= hi_b) & (k >= lo_b);
+        s[nt][c] = va ? s[nt][c] * scale2 : -INFINITY;
+        s[nt][2 + c] = vb ? s[nt][2 + c] * scale2 : -INFINITY;
+        mx_a = fmaxf(mx_a, s[nt][c]);
+        mx_b = fmaxf(mx_b, s[nt][2 + c]);
+      }
+    }
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+    mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+    mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+    const float m_a = fmaxf(m_run[0], mx_a), m_b = fmaxf(m_run[1], mx_b);
+    // a row that has seen no key yet keeps exp(-inf - -inf) out of the way
+    const float base_a = m_a == -INFINITY ? 0.f : m_a, base_b = m_b == -INFINITY ? 0.f : m_b;
+    const float corr_a = fast_exp2(m_run[0] - base_a), corr_b = fast_exp2(m_run[1] - base_b);
+    float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < LA_KEYS / 8; ++nt) {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        s[nt][c] = fast_exp2(s[nt][c] - base_a);
+        s[nt][2 + c] = fast_exp2(s[nt][2 + c] - base_b);
+        sum_a += s[nt][c];
+        sum_b += s[nt][2 + c];
+      }
+    }
+    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+    sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+    sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+    l_run[0] = l_run[0] * corr_a + sum_a;
+    l_run[1] = l_run[1] * corr_b + sum_b;
+    m_run[0] = m_a;
+    m_run[1] = m_b;
+#pragma unroll
+    for (int dt = 0; dt < 2 * VT; ++dt) {
+      o[dt][0] *= corr_a;
+      o[dt][1] *= corr_a;
+      o[dt][2] *= corr_b;
+      o[dt][3] *= corr_b;
+    }
+    // o += weights . values, 16 keys at a time; a key's value is the head of its row
+#pragma unroll
+    for (int kk = 0; kk < LA_KEYS / 16; ++kk) {
+      const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+      const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+      uint32_t r0 = 0, r1 = 0, r2 = 0, r3 = 0;   // what the rounding left of each weight, as a second operand
+      if (p.split_p) {
+        r0 = pack_rest(s[2 * kk][0], s[2 * kk][1], a0); r1 = pack_rest(s[2 * kk][2], s[2 * kk][3], a1);
+        r2 = pack_rest(s[2 * kk + 1][0], s[2 * kk + 1][1], a2); r3 = pack_rest(s[2 * kk + 1][2], s[2 * kk + 1][3], a3);
+      }
+      const int key = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+#pragma unroll
+      for (int dp = 0; dp < VT; ++dp) {   // two 8-wide output tiles per ldmatrix
+        if (dp * 16 < p.kv_rank) {
+          uint32_t b0, b1, b2, b3;
+          ldmatrix_x4_trans(kt + uint32_t(key * rs + (dp * 2 + (lane >> 4)) * 16), b0, b1, b2, b3);
+          mma_bf16(o[2 * dp], a0, a1, a2, a3, b0, b1);
+          mma_bf16(o[2 * dp + 1], a0, a1, a2, a3, b2, b3);
+          if (p.split_p) {
+            mma_bf16(o[2 * dp], r0, r1, r2, r3, b0, b1);
+            mma_bf16(o[2 * dp + 1], r0, r1, r2, r3, b2, b3);
+          }
+        }
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (tok_r[r] < 0) continue;
+    const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+    bf16* dst = p.out + size_t(t0 + tok_r[r]) * p.out_stride + size_t(h0 + head_r[r]) * p.kv_rank;
+#pragma unroll
+    for (int dt = 0; dt < 2 * VT; ++dt) {
+      const int d = dt * 8 + 2 * tq;
+      const float y0 = o[dt][2 * r] * inv, y1 = o[dt][2 * r + 1] * inv;
+      if (p.out_vec && d + 1 < p.kv_rank) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(y0, y1);
+      } else {
+        if (d < p.kv_rank) dst[d] = from_float<bf16>(y0);
+        if (d + 1 < p.kv_rank) dst[d + 1] = from_float<bf16>(y1);
+      }
+    }
+  }
+}
+
 }  // namespace
 
 // buf [n_rows, >= kv_col + kv_rank + rot_dim] with row stride `row_stride`: n_heads query heads of q_head_dim numbers (of
@@ -180,5 +432,62 @@ extern "C" int r2_head_linear(const void* a, int a_stride, int a_head, const voi
   } else {
     return R2_BAD_DTYPE;
   }
+  return launch_status();
+}
+
+// How many (token, head) pairs of a CTA's 64 rows are heads: all heads, or an even share of them where there are more than 64.
+static inline void latent_tile_shape(int n_heads, int* heads_here, int* tokens_here, int* head_groups) {
+  *head_groups = (n_heads + LA_ROWS - 1) / LA_ROWS;
+  *heads_here = (n_heads + *head_groups - 1) / *head_groups;
+  *tokens_here = LA_ROWS / *heads_here;
+}
+
+template <int VT>
+static void launch_latent_attention(const LatentAttnParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+  static bool raised = false;   // the largest rows need more shared memory than a kernel gets unasked
+  if (!raised) {
+    if (cudaFuncSetAttribute(latent_attention_kernel<VT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (LA_ROWS + 2 * LA_KEYS) * (256 * 2 + 16)) != cudaSuccess) return;
+    raised = true;
+  }
+  r2_launch(latent_attention_kernel<VT>, grid, dim3(LA_WARPS * 32), smem, stream, p);
+}
+
+// CTAs along x for n_rows rows in n_entries entries: the sum over entries of ceil(rows / tokens_here) is at most this.
+extern "C" int r2_latent_attention_tiles(int n_rows, int n_entries, int n_heads) {
+  int hh, th, hg;
+  latent_tile_shape(n_heads, &hh, &th, &hg);
+  return (n_rows + n_entries * (th - 1)) / th;
+}
+
+// q [n_rows, n_heads * row] bfloat16 (a head's query against a cache row: kv_rank numbers against the latent, the rest
+// against the shared key part), out [n_rows, n_heads * kv_rank], cache rows of `row` numbers, page_size of them a page.
+// Entry e has the rows q_start[e] .. q_start[e + 1] - 1 at consecutive positions and its block table's row e.
+extern "C" int r2_latent_attention(const void* q, int q_stride, void* out, int out_stride, const void* cache, long long page_stride,
+                                   int page_size, int n_pages, const int32_t* block_tables, int table_width, const int32_t* q_start,
+                                   const int32_t* positions, const int32_t* seq_lens, int n_entries, int n_rows, int n_heads, int row,
+                                   int kv_rank, float scale, int window, int split_p, cudaStream_t stream) {
+  if (n_rows <= 0 || n_entries <= 0) return R2_OK;
+  if (n_heads < 1 || kv_rank < 1 || kv_rank > row || row > 256 || page_size < 1 || window < 0) return R2_BAD_SHAPE;
+  LatentAttnParams p;
+  p.q = (const bf16*)q; p.q_stride = q_stride;
+  p.out = (bf16*)out; p.out_stride = out_stride;
+  p.cache = (const bf16*)cache; p.page_stride = page_stride; p.page_size = page_size; p.page_shift = page_shift_of(page_size);
+  p.n_pages = n_pages; p.block_tables = block_tables; p.table_width = table_width;
+  p.q_start = q_start; p.positions = positions; p.seq_lens = seq_lens; p.n_entries = n_entries;
+  int head_groups;
+  latent_tile_shape(n_heads, &p.heads_here, &p.tokens_here, &head_groups);
+  p.n_heads = n_heads;
+  p.row = row; p.kv_rank = kv_rank; p.row_pad = (row + 15) / 16 * 16;
+  p.scale = scale; p.window = window; p.split_p = split_p;
+  p.q_vec = (uintptr_t(q) % 16 == 0 && q_stride % 8 == 0 && row % 8 == 0) ? 1 : 0;
+  p.k_vec = (uintptr_t(cache) % 16 == 0 && page_stride % 8 == 0 && row % 8 == 0) ? 1 : 0;
+  p.out_vec = (uintptr_t(out) % 4 == 0 && out_stride % 2 == 0 && kv_rank % 2 == 0) ? 1 : 0;
+  const size_t smem = size_t(LA_ROWS + 2 * LA_KEYS) * (p.row_pad * 2 + 16);
+  const dim3 grid((n_rows + n_entries * (p.tokens_here - 1)) / p.tokens_here, head_groups);
+  if (kv_rank <= 64) launch_latent_attention<4>(p, grid, smem, stream);
+  else if (kv_rank <= 128) launch_latent_attention<8>(p, grid, smem, stream);
+  else if (kv_rank <= 192) launch_latent_attention<12>(p, grid, smem, stream);
+  else launch_latent_attention<16>(p, grid, smem, stream);
   return launch_status();
 }

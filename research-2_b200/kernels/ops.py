@@ -1062,7 +1062,8 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     (float32 [T, n_heads]) multiplies head h's output by the sigmoid of its entry: these three are taken by the general
     kernel, the mma.sync prefill kernel and the fused decode kernel.
     `values_in_keys`: the cache holds key rows only and a key's first v_head_dim numbers are its value (a cache of
-    latents; `v_cache` is not read); the general kernel takes it.
+    latents; `v_cache` is not read); the general kernel takes it, and for bfloat16 with one key head and `q_start` the
+    latent kernel, whose tiles hold all heads of a few tokens.
     `decode_only` says that every row is an entry of its own (one new token each) and
     `max_context` bounds the rows' context lengths; `q_start` (int32 [R + 1]) with `n_tiles`, the
     sum over entries of ceil(rows / 64), lets the tensor-core prefill kernel take the batch. They
@@ -1147,6 +1148,17 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             _p(head_gate), head_gate_stride, _stream())
         _check(status, "paged_attention (prefill)")
         _used("attention_prefill")
+        return out
+    if (values_in_keys and n_kv_heads == 1 and q.dtype == torch.bfloat16 and _fast_attention and q_start is not None and keep_first == 0
+            and not sink and gate is None and not capped and head_dim <= 256 and v_head_dim <= head_dim):
+        # a cache of latents: every head reads the same rows, so a tile's rows are (token, head) pairs (mma.sync)
+        _need(q_start, "q_start", torch.int32, 1)
+        status = _lib("latent_attention").r2_latent_attention(
+            _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), C.c_longlong(page_stride), page_size, n_pages,
+            _p(block_tables), block_tables.shape[1], _p(q_start), _p(positions), _p(seq_lens), q_start.shape[0] - 1, n, n_heads,
+            head_dim, v_head_dim, C.c_float(scale), window, int(_exact_weights), _stream())
+        _check(status, "paged_attention (latents)")
+        _used("latent_attention")
         return out
     status = _lib("attention_simt").r2_attention_simt(
         _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), _p(k_cache if values_in_keys else v_cache), C.c_longlong(page_stride),

@@ -240,6 +240,68 @@ def test_latent_rows_and_the_products_per_head(dtype, shape):
     close(out, torch.einsum("thc,hvc->thv", mixed.double().view(rows, heads, rank), w_uv.double().view(heads, vdim, rank)).reshape(rows, -1), dtype, "values")
 
 
+def plain_attention_over_latents(q, rows_of, positions, kv_rank, scale, window):
+    """q [T, H, row] float64, rows_of[t]: the cache rows [len, row] of the token's sequence, positions[t]: the token's place.
+    Head h of token t: softmax over the keys (p - window, p] of scale * q . row, times the rows' first kv_rank numbers."""
+    out = torch.zeros(q.shape[0], q.shape[1], kv_rank, dtype=F64)
+    for t in range(q.shape[0]):
+        p = positions[t]
+        first = max(0, p - window + 1) if window else 0
+        keys = rows_of[t][first: p + 1]
+        weights = torch.softmax((q[t] @ keys.T) * scale, dim=-1)
+        out[t] = weights @ keys[:, :kv_rank]
+    return out
+
+
+# heads, cache row, latent's part of it, window, page size
+LATENT_SHAPES = [(12, 160, 128, 64, 16), (3, 40, 24, 0, 8), (5, 33, 20, 7, 3), (70, 48, 48, 100, 32), (1, 256, 200, 1, 16), (16, 96, 64, 63, 64),
+                 (64, 24, 16, 65, 4), (2, 136, 130, 129, 128)]
+
+
+@pytest.mark.parametrize("cut", ["prompts", "decoded", "portions"])
+@pytest.mark.parametrize("shape", LATENT_SHAPES)
+def test_attention_over_a_cache_of_latents(shape, cut):
+    """The bfloat16 kernel whose tiles hold all heads of a few tokens, alone: entries of unequal lengths whose pages lie
+    scattered in a pool full of large numbers, as whole prompts, as single decoded tokens and as portions that start in the
+    middle; windows that end inside, at and beyond a tile of 64 keys; rows that are no multiple of 8 or 16 numbers."""
+    from research_2_b200.kernels import ops
+
+    heads, row, rank, window, page = shape
+    gen = torch.Generator().manual_seed(heads * 1000 + row)
+    lengths = [1, 2, 63, 64, 65, 130, 200]
+    scale = 1.0 / math.sqrt(row)
+    per_seq = [(torch.randn(n, row, generator=gen) * 1.5).to(torch.bfloat16) for n in lengths]
+    table_width = max(-(-n // page) for n in lengths)
+    n_pages = 1 + len(lengths) * table_width
+    order = (torch.randperm(n_pages - 1, generator=gen) + 1).tolist()
+    cache = torch.full((n_pages, page, row), 300.0, dtype=torch.bfloat16)
+    tables = torch.zeros(len(lengths), table_width, dtype=torch.int32)
+    for e, (n, rows_) in enumerate(zip(lengths, per_seq)):
+        for b in range(-(-n // page)):
+            tables[e, b] = order.pop()
+            piece = rows_[b * page: (b + 1) * page]
+            cache[tables[e, b], : piece.shape[0]] = piece
+    if cut == "prompts":
+        spans = [(0, n) for n in lengths]
+    elif cut == "decoded":
+        spans = [(n - 1, n) for n in lengths]
+    else:
+        spans = [(n // 3, n - n // 4) for n in lengths]
+    entry_rows = [b - a for a, b in spans]
+    q_start = [sum(entry_rows[:i]) for i in range(len(lengths) + 1)]
+    positions = [p for a, b in spans for p in range(a, b)]
+    row_entry = [e for e, (a, b) in enumerate(spans) for _ in range(a, b)]
+    q = (torch.randn(len(positions), heads * row, generator=gen) * 1.5).to(torch.bfloat16)
+    want = plain_attention_over_latents(q.double().view(-1, heads, row), [per_seq[e].double() for e in row_entry], positions, rank, scale, window)
+    before = ops.kernel_uses().get("latent_attention", 0)
+    got = ops.paged_attention(
+        q.to(DEV), cache.to(DEV), cache.to(DEV), page * row, page, n_pages, tables.to(DEV), i32(row_entry), i32(positions),
+        i32([b for _, b in spans]), heads, 1, row, scale, window, decode_only=cut == "decoded", max_context=max(lengths),
+        q_start=i32(q_start), n_tiles=sum(-(-r // 64) for r in entry_rows), v_head_dim=rank, values_in_keys=True)
+    assert ops.kernel_uses().get("latent_attention", 0) == before + 1, "another kernel took the call"
+    close(got.view(-1, heads, rank), want, torch.bfloat16, f"{shape} {cut}")
+
+
 # ---------------------------------------------------------------------------------------------
 # one key that stands out, at every edge
 
