@@ -151,6 +151,7 @@ latent_prepare_kernel(T* __restrict__ buf, int row_stride, int n_heads, int q_he
 // masked in float (causal, window, context length), the softmax is online, and its weights enter the second product
 // rounded to bfloat16, or with `split_p` as the sum of two bfloat16 numbers. VT: 16-wide column tiles of the output.
 constexpr int LA_WARPS = 4, LA_ROWS = 64, LA_KEYS = 64;
+static_assert(LA_WARPS * 32 == 2 * LA_KEYS, "the copy of a key tile gives two threads to a key");
 
 struct LatentAttnParams {
   const bf16* q; int q_stride;
@@ -171,6 +172,85 @@ __device__ __forceinline__ uint4 eight_of(const bf16* src_row, int c, int row, b
 #pragma unroll
   for (int i = 0; i < 8; ++i) tmp[i] = c * 8 + i < row ? src_row[c * 8 + i] : from_float<bf16>(0.f);
   return *reinterpret_cast<const uint4*>(tmp);
+}
+
+// The small products per head for bfloat16 on the warp-level tensor cores: a CTA has 64 rows x 64 columns of one head (16 rows
+// to a warp), K in pieces of 64 through shared memory. A head's matrix [N][K] is read like keys (ldmatrix as it lies), [K][N]
+// like values (ldmatrix transposed). An output's sum depends on K alone: float sums in the order of the 16-wide steps.
+constexpr int HM_TILE = 64, HM_PAD = HM_TILE + 8;
+
+struct HeadLinearParams {
+  const bf16* a; int a_stride, a_head;
+  const bf16* w; int w_is_nk;
+  bf16* out; int out_stride, out_head;
+  int n_rows, k_total, n_total;
+  int a_vec, w_vec, out_vec;   // 16-byte loads of a's / of w's rows, 4-byte stores of outputs are possible
+};
+
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(const HeadLinearParams p) {
+  using namespace r2ptx;
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ __align__(16) bf16 a_s[HM_TILE][HM_PAD];
+  __shared__ __align__(16) bf16 w_s[HM_TILE][HM_PAD];
+  const int h = blockIdx.z, r0 = blockIdx.x * HM_TILE, c0 = blockIdx.y * HM_TILE;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bf16* ah = p.a + size_t(h) * p.a_head;
+  const bf16* wh = p.w + size_t(h) * p.k_total * p.n_total;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  float acc[HM_TILE / 8][4];
+#pragma unroll
+  for (int i = 0; i < HM_TILE / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const bool warp_has_rows = r0 + warp * 16 < p.n_rows;
+  for (int k0 = 0; k0 < p.k_total; k0 += HM_TILE) {
+    __syncthreads();
+    for (int idx = tid; idx < HM_TILE * (HM_TILE / 8); idx += 128) {
+      const int r = idx / (HM_TILE / 8), c = idx % (HM_TILE / 8);
+      uint4 av = zero4, wv = zero4;
+      if (r0 + r < p.n_rows) av = eight_of(ah + size_t(r0 + r) * p.a_stride + k0, c, p.k_total - k0, p.a_vec != 0);
+      if (p.w_is_nk) {   // r: a column of the output, its K numbers lie side by side
+        if (c0 + r < p.n_total) wv = eight_of(wh + size_t(c0 + r) * p.k_total + k0, c, p.k_total - k0, p.w_vec != 0);
+      } else {           // r: one of the K, the output's columns lie side by side
+        if (k0 + r < p.k_total) wv = eight_of(wh + size_t(k0 + r) * p.n_total + c0, c, p.n_total - c0, p.w_vec != 0);
+      }
+      *reinterpret_cast<uint4*>(&a_s[r][c * 8]) = av;
+      *reinterpret_cast<uint4*>(&w_s[r][c * 8]) = wv;
+    }
+    __syncthreads();
+    if (!warp_has_rows) continue;
+#pragma unroll
+    for (int ks = 0; ks < HM_TILE / 16; ++ks) {
+      uint32_t a0, a1, a2, a3;
+      ldmatrix_x4(smem_u32(&a_s[warp * 16 + (lane & 15)][ks * 16 + 8 * (lane >> 4)]), a0, a1, a2, a3);
+#pragma unroll
+      for (int np = 0; np < HM_TILE / 16; ++np) {
+        uint32_t b0, b1, b2, b3;
+        if (p.w_is_nk) ldmatrix_x4(smem_u32(&w_s[np * 16 + (lane & 7) + 8 * (lane >> 4)][ks * 16 + 8 * ((lane >> 3) & 1)]), b0, b1, b2, b3);
+        else ldmatrix_x4_trans(smem_u32(&w_s[ks * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)][np * 16 + 8 * (lane >> 4)]), b0, b1, b2, b3);
+        mma_bf16(acc[2 * np], a0, a1, a2, a3, b0, b1);
+        mma_bf16(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+      }
+    }
+  }
+  const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int r = r0 + warp * 16 + g + 8 * half;
+    if (r >= p.n_rows) continue;
+    bf16* dst = p.out + size_t(r) * p.out_stride + size_t(h) * p.out_head;
+#pragma unroll
+    for (int nt = 0; nt < HM_TILE / 8; ++nt) {
+      const int n = c0 + nt * 8 + 2 * tq;
+      const float y0 = acc[nt][2 * half], y1 = acc[nt][2 * half + 1];
+      if (p.out_vec && n + 1 < p.n_total) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + n) = __floats2bfloat162_rn(y0, y1);
+      } else {
+        if (n < p.n_total) dst[n] = from_float<bf16>(y0);
+        if (n + 1 < p.n_total) dst[n + 1] = from_float<bf16>(y1);
+      }
+    }
+  }
 }
 
 template <int VT>
@@ -221,21 +301,20 @@ latent_attention_kernel(const LatentAttnParams p) {
     *reinterpret_cast<uint4*>(q_s + m * rs + c * 16) = v;
   }
   auto load_keys = [&](int it, int buf) {
-    const int j0 = lo + it * LA_KEYS;
-    uint8_t* tile = k_s + buf * (LA_KEYS * rs);
-    for (int idx = tid; idx < LA_KEYS * chunks; idx += LA_WARPS * 32) {
-      const int key = idx / chunks, c = idx - key * chunks;
-      const int j = j0 + key;
-      uint8_t* dst = tile + key * rs + c * 16;
-      if (j <= hi) {
-        int page = table[page_index(j, p.page_size, p.page_shift)];
-        page = (page < 0 || page >= p.n_pages) ? 0 : page;
-        const bf16* src = p.cache + size_t(page) * p.page_stride + size_t(page_offset(j, p.page_size, p.page_shift)) * p.row;
-        if (p.k_vec && c * 8 + 8 <= p.row) cp_async16(smem_u32(dst), src + c * 8, true);
-        else *reinterpret_cast<uint4*>(dst) = eight_of(src, c, p.row, false);
-      } else {
-        *reinterpret_cast<uint4*>(dst) = zero4;   // no row sees it: zeros, whatever the cache holds there
+    // two threads a key: one look into the block table per key, then its pieces one after the other
+    const int key = tid >> 1;
+    const int j = lo + it * LA_KEYS + key;
+    uint8_t* dst = k_s + buf * (LA_KEYS * rs) + key * rs;
+    if (j <= hi) {
+      int page = table[page_index(j, p.page_size, p.page_shift)];
+      page = (page < 0 || page >= p.n_pages) ? 0 : page;
+      const bf16* src = p.cache + size_t(page) * p.page_stride + size_t(page_offset(j, p.page_size, p.page_shift)) * p.row;
+      for (int c = tid & 1; c < chunks; c += 2) {
+        if (p.k_vec && c * 8 + 8 <= p.row) cp_async16(smem_u32(dst + c * 16), src + c * 8, true);
+        else *reinterpret_cast<uint4*>(dst + c * 16) = eight_of(src, c, p.row, false);
       }
+    } else {
+      for (int c = tid & 1; c < chunks; c += 2) *reinterpret_cast<uint4*>(dst + c * 16) = zero4;   // no row sees it: zeros, whatever the cache holds there
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -427,8 +506,16 @@ extern "C" int r2_head_linear(const void* a, int a_stride, int a_head, const voi
     r2_launch(head_linear_kernel<float>, grid, dim3(256), size_t(0), stream, (const float*)a, a_stride, a_head, (const float*)w, w_is_nk,
               (float*)out, out_stride, out_head, n_rows, k, n);
   } else if (dtype == R2_BF16) {
-    r2_launch(head_linear_kernel<bf16>, grid, dim3(256), size_t(0), stream, (const bf16*)a, a_stride, a_head, (const bf16*)w, w_is_nk,
-              (bf16*)out, out_stride, out_head, n_rows, k, n);
+    HeadLinearParams p;
+    p.a = (const bf16*)a; p.a_stride = a_stride; p.a_head = a_head;
+    p.w = (const bf16*)w; p.w_is_nk = w_is_nk;
+    p.out = (bf16*)out; p.out_stride = out_stride; p.out_head = out_head;
+    p.n_rows = n_rows; p.k_total = k; p.n_total = n;
+    p.a_vec = (uintptr_t(a) % 16 == 0 && a_stride % 8 == 0 && a_head % 8 == 0) ? 1 : 0;
+    p.w_vec = (uintptr_t(w) % 16 == 0 && (w_is_nk ? k : n) % 8 == 0 && (size_t(k) * n) % 8 == 0) ? 1 : 0;
+    p.out_vec = (uintptr_t(out) % 4 == 0 && out_stride % 2 == 0 && out_head % 2 == 0) ? 1 : 0;
+    r2_launch(head_linear_mma_kernel, dim3((n_rows + HM_TILE - 1) / HM_TILE, (n + HM_TILE - 1) / HM_TILE, n_heads), dim3(128), size_t(0),
+              stream, p);
   } else {
     return R2_BAD_DTYPE;
   }

@@ -98,11 +98,12 @@ def test_activations_and_norms_around_a_sublayer(dtype):
     from research_2_b200.kernels import ops
 
     gen = torch.Generator().manual_seed(2)
-    z = (torch.randn(23, 52, generator=gen) * 3).to(dtype)
-    z[0, :4] = torch.tensor([0.0, -0.0, 1e-3, -1e-3]).to(dtype)
-    for p, q in ((0.3, -0.2), (-4.0, 2.5)):
-        a_pos, a_neg = math.log1p(math.exp(p)), 0.5 + math.log1p(math.exp(q))
-        close(ops.xielu(z.to(DEV), a_pos, a_neg), plain.xielu(z.double(), p, q), dtype, "xielu")
+    for width in (52, 24, 2056, 3):   # rows of pairs, of 16-byte pieces (in one and in two blocks), of single numbers
+        z = (torch.randn(23, width, generator=gen) * 3).to(dtype)
+        z[0, :3] = torch.tensor([-0.0, 1e-3, -1e-3]).to(dtype)
+        for p, q in ((0.3, -0.2), (-4.0, 2.5)):
+            a_pos, a_neg = math.log1p(math.exp(p)), 0.5 + math.log1p(math.exp(q))
+            close(ops.xielu(z.to(DEV), a_pos, a_neg), plain.xielu(z.double(), p, q), dtype, f"xielu {width}")
     # gated silu units of several experts with routing weights, and a tail (the expert that every row uses) with a gate per row
     rows, experts, width, tail = 21, 3, 10, 7
     inner = experts * width + tail
@@ -197,7 +198,7 @@ def test_latent_rows_and_the_products_per_head(dtype, shape):
 
     heads, dim, rot_dim, rot_dims, rank, vdim = shape
     gen = torch.Generator().manual_seed(6)
-    rows, page, eps, magnitude = 19, 4, 1e-4, 1.17
+    rows, page, eps, magnitude = 83, 4, 1e-4, 1.17
     q_head, row = dim + rot_dim, rank + rot_dim
     proj = torch.randn(rows, heads * q_head + row + 5, generator=gen).to(dtype)
     positions = torch.randint(0, 3000, (rows,), generator=gen).tolist()
@@ -208,7 +209,7 @@ def test_latent_rows_and_the_products_per_head(dtype, shape):
     down = proj[:, heads * q_head: heads * q_head + row].double()
     want_c = plain.unit_rms(down[:, :rank], eps) * norm_w.double()
     want_k_rot = plain.rotate(down[:, rank:], positions, freqs, "interleaved", magnitude)
-    n_pages = 8
+    n_pages = 24
     cache = torch.full((n_pages * page * row,), 7.0, dtype=dtype, device=DEV)
     slots = torch.randperm((n_pages - 1) * page, generator=gen)[:rows] + page
     queries = torch.zeros(rows, heads * row, dtype=dtype, device=DEV)
