@@ -253,10 +253,11 @@ head_linear_mma_kernel(const HeadLinearParams p) {
   }
 }
 
-template <int VT>
+template <int VT, bool SPLIT>
 __global__ void __launch_bounds__(LA_WARPS * 32)
 latent_attention_kernel(const LatentAttnParams p) {
   using namespace r2ptx;
+  constexpr int NP = SPLIT ? 1 : LA_KEYS / 16;   // 16-key pieces of a tile that a warp takes
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) uint8_t la_smem[];
@@ -265,16 +266,42 @@ latent_attention_kernel(const LatentAttnParams p) {
   uint8_t* q_s = la_smem;
   uint8_t* k_s = la_smem + LA_ROWS * rs;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (tid == 0) {   // which entry, and which of its tiles, this CTA has
-    int left = blockIdx.x, found = -1, first = 0;
-    for (int e = 0; e < p.n_entries; ++e) {
-      const int n = p.q_start[e + 1] - p.q_start[e];
-      const int tiles = (n + p.tokens_here - 1) / p.tokens_here;
-      if (left < tiles) { found = e; first = p.q_start[e] + left * p.tokens_here; break; }
-      left -= tiles;
+  const int row0 = SPLIT ? 0 : warp * 16;   // the warp's first row of the tile, and its first key of a key tile
+  const int key0 = SPLIT ? warp * 16 : 0;
+  if (warp == 0) {   // which entry, and which of its tiles, this CTA has: 32 entries at a time, their tiles summed by shuffles
+    int found = -1, first = 0;
+    if (SPLIT) {     // every entry is one row
+      if (int(blockIdx.x) < p.n_entries) { found = blockIdx.x; first = blockIdx.x; }
+    } else {
+      int base = 0;
+      for (int e0 = 0; e0 < p.n_entries && found < 0; e0 += 32) {
+        const int cand = e0 + lane;
+        int start = 0, tiles = 0;
+        if (cand < p.n_entries) {
+          start = p.q_start[cand];
+          tiles = (p.q_start[cand + 1] - start + p.tokens_here - 1) / p.tokens_here;
+        }
+        int upto = tiles;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, upto, d);
+          if (lane >= d) upto += v;
+        }
+        const int before = base + upto - tiles;
+        const bool mine = int(blockIdx.x) >= before && int(blockIdx.x) < before + tiles;
+        const unsigned who = __ballot_sync(0xffffffffu, mine);
+        if (who != 0u) {
+          const int src = __ffs(who) - 1;
+          found = __shfl_sync(0xffffffffu, cand, src);
+          first = __shfl_sync(0xffffffffu, start + (int(blockIdx.x) - before) * p.tokens_here, src);
+        }
+        base += __shfl_sync(0xffffffffu, upto, 31);
+      }
     }
-    tile_info[0] = found;
-    tile_info[1] = first;
+    if (lane == 0) {
+      tile_info[0] = found;
+      tile_info[1] = first;
+    }
   }
   __syncthreads();
   const int e = tile_info[0];
@@ -292,7 +319,7 @@ latent_attention_kernel(const LatentAttnParams p) {
   const int chunks = p.row_pad / 8;
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 
-  for (int idx = tid; idx < LA_ROWS * chunks; idx += LA_WARPS * 32) {
+  for (int idx = tid; idx < (SPLIT ? 16 : LA_ROWS) * chunks; idx += LA_WARPS * 32) {
     const int m = idx / chunks, c = idx - m * chunks;
     const int tok = m / p.heads_here, hh = m - tok * p.heads_here;
     uint4 v = zero4;
@@ -324,7 +351,7 @@ latent_attention_kernel(const LatentAttnParams p) {
   int pos_r[2], tok_r[2], head_r[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    const int m = warp * 16 + g + 8 * r;
+    const int m = row0 + g + 8 * r;
     tok_r[r] = m / p.heads_here;
     head_r[r] = m - tok_r[r] * p.heads_here;
     const bool valid = tok_r[r] < n_tok && head_r[r] < n_heads_here;
@@ -332,7 +359,7 @@ latent_attention_kernel(const LatentAttnParams p) {
     if (!valid) tok_r[r] = -1;
   }
   // the positions that this warp's rows span (none: the warp only helps to copy)
-  const int w_tok_first = (warp * 16) / p.heads_here, w_tok_last = min((warp * 16 + 15) / p.heads_here, n_tok - 1);
+  const int w_tok_first = row0 / p.heads_here, w_tok_last = min((row0 + 15) / p.heads_here, n_tok - 1);
   const bool warp_has_rows = w_tok_first < n_tok;
   const int w_pmin = warp_has_rows ? p.positions[t0 + w_tok_first] : 0, w_pmax = warp_has_rows ? p.positions[t0 + w_tok_last] : -1;
 
@@ -349,19 +376,19 @@ latent_attention_kernel(const LatentAttnParams p) {
     __syncthreads();   // tile `it` (and, the first time, the queries) is there; nobody reads the other buffer any more
     if (it + 1 < n_tiles) load_keys(it + 1, (it + 1) & 1);
     const int j0 = lo + it * LA_KEYS;
-    if (!warp_has_rows || j0 > w_pmax || (p.window > 0 && j0 + LA_KEYS - 1 <= w_pmin - p.window)) continue;
+    if (!warp_has_rows || j0 + key0 > w_pmax || (p.window > 0 && j0 + key0 + 16 * NP - 1 <= w_pmin - p.window)) continue;
     const uint32_t kt = smem_u32(k_s) + uint32_t((it & 1) * (LA_KEYS * rs));
-    float s[LA_KEYS / 8][4];
+    float s[2 * NP][4];
 #pragma unroll
-    for (int nt = 0; nt < LA_KEYS / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    for (int nt = 0; nt < 2 * NP; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll 2
     for (int ks = 0; ks < k_steps; ++ks) {
       uint32_t a0, a1, a2, a3;
-      ldmatrix_x4(smem_u32(q_s) + uint32_t((warp * 16 + (lane & 15)) * rs + (ks * 16 + 8 * (lane >> 4)) * 2), a0, a1, a2, a3);
+      ldmatrix_x4(smem_u32(q_s) + uint32_t((row0 + (lane & 15)) * rs + (ks * 16 + 8 * (lane >> 4)) * 2), a0, a1, a2, a3);
 #pragma unroll
-      for (int np = 0; np < LA_KEYS / 16; ++np) {   // two 8-key tiles per ldmatrix
+      for (int np = 0; np < NP; ++np) {   // two 8-key tiles per ldmatrix
         uint32_t b0, b1, b2, b3;
-        const int key = np * 16 + (lane & 7) + 8 * (lane >> 4);
+        const int key = key0 + np * 16 + (lane & 7) + 8 * (lane >> 4);
         ldmatrix_x4(kt + uint32_t(key * rs + (ks * 2 + ((lane >> 3) & 1)) * 16), b0, b1, b2, b3);
         mma_bf16(s[2 * np], a0, a1, a2, a3, b0, b1);
         mma_bf16(s[2 * np + 1], a0, a1, a2, a3, b2, b3);
@@ -372,10 +399,10 @@ latent_attention_kernel(const LatentAttnParams p) {
     const int lo_a = p.window > 0 ? pos_r[0] - p.window + 1 - j0 : INT_MIN, lo_b = p.window > 0 ? pos_r[1] - p.window + 1 - j0 : INT_MIN;
     float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-    for (int nt = 0; nt < LA_KEYS / 8; ++nt) {
+    for (int nt = 0; nt < 2 * NP; ++nt) {
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const int k = nt * 8 + 2 * tq + c;
+        const int k = key0 + nt * 8 + 2 * tq + c;
         const bool va = (k <= hi_a) & (k >= lo_a), vb = (k <= hi_b) & (k >= lo_b);
         s[nt][c] = va ? s[nt][c] * scale2 : -INFINITY;
         s[nt][2 + c] = vb ? s[nt][2 + c] * scale2 : -INFINITY;
@@ -393,7 +420,7 @@ latent_attention_kernel(const LatentAttnParams p) {
     const float corr_a = fast_exp2(m_run[0] - base_a), corr_b = fast_exp2(m_run[1] - base_b);
     float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
-    for (int nt = 0; nt < LA_KEYS / 8; ++nt) {
+    for (int nt = 0; nt < 2 * NP; ++nt) {
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         s[nt][c] = fast_exp2(s[nt][c] - base_a);
@@ -419,7 +446,7 @@ latent_attention_kernel(const LatentAttnParams p) {
     }
     // o += weights . values, 16 keys at a time; a key's value is the head of its row
 #pragma unroll
-    for (int kk = 0; kk < LA_KEYS / 16; ++kk) {
+    for (int kk = 0; kk < NP; ++kk) {
       const uint32_t a0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]), a1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
       const uint32_t a2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]), a3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
       uint32_t r0 = 0, r1 = 0, r2 = 0, r3 = 0;   // what the rounding left of each weight, as a second operand
@@ -427,7 +454,7 @@ latent_attention_kernel(const LatentAttnParams p) {
         r0 = pack_rest(s[2 * kk][0], s[2 * kk][1], a0); r1 = pack_rest(s[2 * kk][2], s[2 * kk][3], a1);
         r2 = pack_rest(s[2 * kk + 1][0], s[2 * kk + 1][1], a2); r3 = pack_rest(s[2 * kk + 1][2], s[2 * kk + 1][3], a3);
       }
-      const int key = kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
+      const int key = key0 + kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1);
 #pragma unroll
       for (int dp = 0; dp < VT; ++dp) {   // two 8-wide output tiles per ldmatrix
         if (dp * 16 < p.kv_rank) {
@@ -445,20 +472,57 @@ latent_attention_kernel(const LatentAttnParams p) {
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
 
+  if constexpr (SPLIT) {
+    // the four warps hold the same 16 rows over different keys: their maxima, sums and outputs meet in shared memory
+    constexpr int PW = VT * 16 + 2;
+    float* part = reinterpret_cast<float*>(k_s);   // [warp][row][outputs, maximum, sum]
+    __syncthreads();   // nobody reads a key tile any more
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    if (tok_r[r] < 0) continue;
-    const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
-    bf16* dst = p.out + size_t(t0 + tok_r[r]) * p.out_stride + size_t(h0 + head_r[r]) * p.kv_rank;
+    for (int r = 0; r < 2; ++r) {
+      float* mine = part + (warp * 16 + g + 8 * r) * PW;
 #pragma unroll
-    for (int dt = 0; dt < 2 * VT; ++dt) {
-      const int d = dt * 8 + 2 * tq;
-      const float y0 = o[dt][2 * r] * inv, y1 = o[dt][2 * r + 1] * inv;
-      if (p.out_vec && d + 1 < p.kv_rank) {
-        *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(y0, y1);
-      } else {
-        if (d < p.kv_rank) dst[d] = from_float<bf16>(y0);
-        if (d + 1 < p.kv_rank) dst[d + 1] = from_float<bf16>(y1);
+      for (int dt = 0; dt < 2 * VT; ++dt) {
+        mine[dt * 8 + 2 * tq] = o[dt][2 * r];
+        mine[dt * 8 + 2 * tq + 1] = o[dt][2 * r + 1];
+      }
+      if (tq == 0) { mine[VT * 16] = m_run[r]; mine[VT * 16 + 1] = l_run[r]; }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < 16 * p.kv_rank; idx += LA_WARPS * 32) {
+      const int m = idx / p.kv_rank, d = idx - m * p.kv_rank;
+      const int tok = m / p.heads_here, hh = m - tok * p.heads_here;
+      if (tok >= n_tok || hh >= n_heads_here) continue;
+      float top = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < LA_WARPS; ++w) top = fmaxf(top, part[(w * 16 + m) * PW + VT * 16]);
+      float sum = 0.f, y = 0.f;
+      if (top != -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < LA_WARPS; ++w) {
+          const float* theirs = part + (w * 16 + m) * PW;
+          const float f = fast_exp2(theirs[VT * 16] - top);
+          sum += theirs[VT * 16 + 1] * f;
+          y += theirs[d] * f;
+        }
+      }
+      p.out[size_t(t0 + tok) * p.out_stride + size_t(h0 + hh) * p.kv_rank + d] = from_float<bf16>(sum > 0.f ? y / sum : 0.f);
+    }
+  } else {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      if (tok_r[r] < 0) continue;
+      const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+      bf16* dst = p.out + size_t(t0 + tok_r[r]) * p.out_stride + size_t(h0 + head_r[r]) * p.kv_rank;
+#pragma unroll
+      for (int dt = 0; dt < 2 * VT; ++dt) {
+        const int d = dt * 8 + 2 * tq;
+        const float y0 = o[dt][2 * r] * inv, y1 = o[dt][2 * r + 1] * inv;
+        if (p.out_vec && d + 1 < p.kv_rank) {
+          *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(y0, y1);
+        } else {
+          if (d < p.kv_rank) dst[d] = from_float<bf16>(y0);
+          if (d + 1 < p.kv_rank) dst[d + 1] = from_float<bf16>(y1);
+        }
       }
     }
   }
@@ -522,39 +586,46 @@ extern "C" int r2_head_linear(const void* a, int a_stride, int a_head, const voi
   return launch_status();
 }
 
-// How many (token, head) pairs of a CTA's 64 rows are heads: all heads, or an even share of them where there are more than 64.
-static inline void latent_tile_shape(int n_heads, int* heads_here, int* tokens_here, int* head_groups) {
-  *head_groups = (n_heads + LA_ROWS - 1) / LA_ROWS;
+// How many (token, head) pairs of a CTA's rows are heads: all heads, or an even share of them where there are more than the
+// tile has rows: 64, or 16 where every entry is one row and the four warps share the keys instead (`single_rows`).
+static inline void latent_tile_shape(int n_heads, int single_rows, int* heads_here, int* tokens_here, int* head_groups) {
+  const int rows = single_rows ? 16 : LA_ROWS;
+  *head_groups = (n_heads + rows - 1) / rows;
   *heads_here = (n_heads + *head_groups - 1) / *head_groups;
-  *tokens_here = LA_ROWS / *heads_here;
+  *tokens_here = single_rows ? 1 : rows / *heads_here;
 }
 
-template <int VT>
-static void launch_latent_attention(const LatentAttnParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
+template <int VT, bool SPLIT>
+static void launch_latent_attention(const LatentAttnParams& p, dim3 grid, cudaStream_t stream) {
+  const size_t rs = p.row_pad * 2 + 16, tiles = 2 * LA_KEYS * rs, parts = size_t(LA_WARPS) * 16 * (VT * 16 + 2) * sizeof(float);
+  const size_t smem = LA_ROWS * rs + (SPLIT && parts > tiles ? parts : tiles);
   static bool raised = false;   // the largest rows need more shared memory than a kernel gets unasked
   if (!raised) {
-    if (cudaFuncSetAttribute(latent_attention_kernel<VT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(latent_attention_kernel<VT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (LA_ROWS + 2 * LA_KEYS) * (256 * 2 + 16)) != cudaSuccess) return;
     raised = true;
   }
-  r2_launch(latent_attention_kernel<VT>, grid, dim3(LA_WARPS * 32), smem, stream, p);
+  r2_launch(latent_attention_kernel<VT, SPLIT>, grid, dim3(LA_WARPS * 32), smem, stream, p);
 }
 
-// CTAs along x for n_rows rows in n_entries entries: the sum over entries of ceil(rows / tokens_here) is at most this.
-extern "C" int r2_latent_attention_tiles(int n_rows, int n_entries, int n_heads) {
-  int hh, th, hg;
-  latent_tile_shape(n_heads, &hh, &th, &hg);
-  return (n_rows + n_entries * (th - 1)) / th;
+template <bool SPLIT>
+static void launch_latent_attention_of(int kv_rank, const LatentAttnParams& p, dim3 grid, cudaStream_t stream) {
+  if (kv_rank <= 64) launch_latent_attention<4, SPLIT>(p, grid, stream);
+  else if (kv_rank <= 128) launch_latent_attention<8, SPLIT>(p, grid, stream);
+  else if (kv_rank <= 192) launch_latent_attention<12, SPLIT>(p, grid, stream);
+  else launch_latent_attention<16, SPLIT>(p, grid, stream);
 }
 
 // q [n_rows, n_heads * row] bfloat16 (a head's query against a cache row: kv_rank numbers against the latent, the rest
 // against the shared key part), out [n_rows, n_heads * kv_rank], cache rows of `row` numbers, page_size of them a page.
-// Entry e has the rows q_start[e] .. q_start[e + 1] - 1 at consecutive positions and its block table's row e.
+// Entry e has the rows q_start[e] .. q_start[e + 1] - 1 at consecutive positions and its block table's row e. `single_rows`: every
+// entry is one row (a decode step); CTAs then have the heads of one token and their warps a quarter of every key tile each.
 extern "C" int r2_latent_attention(const void* q, int q_stride, void* out, int out_stride, const void* cache, long long page_stride,
                                    int page_size, int n_pages, const int32_t* block_tables, int table_width, const int32_t* q_start,
                                    const int32_t* positions, const int32_t* seq_lens, int n_entries, int n_rows, int n_heads, int row,
-                                   int kv_rank, float scale, int window, int split_p, cudaStream_t stream) {
+                                   int kv_rank, float scale, int window, int split_p, int single_rows, cudaStream_t stream) {
   if (n_rows <= 0 || n_entries <= 0) return R2_OK;
+  if (single_rows && n_rows != n_entries) return R2_BAD_SHAPE;
   if (n_heads < 1 || kv_rank < 1 || kv_rank > row || row > 256 || page_size < 1 || window < 0) return R2_BAD_SHAPE;
   LatentAttnParams p;
   p.q = (const bf16*)q; p.q_stride = q_stride;
@@ -563,18 +634,15 @@ extern "C" int r2_latent_attention(const void* q, int q_stride, void* out, int o
   p.n_pages = n_pages; p.block_tables = block_tables; p.table_width = table_width;
   p.q_start = q_start; p.positions = positions; p.seq_lens = seq_lens; p.n_entries = n_entries;
   int head_groups;
-  latent_tile_shape(n_heads, &p.heads_here, &p.tokens_here, &head_groups);
+  latent_tile_shape(n_heads, single_rows, &p.heads_here, &p.tokens_here, &head_groups);
   p.n_heads = n_heads;
   p.row = row; p.kv_rank = kv_rank; p.row_pad = (row + 15) / 16 * 16;
   p.scale = scale; p.window = window; p.split_p = split_p;
   p.q_vec = (uintptr_t(q) % 16 == 0 && q_stride % 8 == 0 && row % 8 == 0) ? 1 : 0;
   p.k_vec = (uintptr_t(cache) % 16 == 0 && page_stride % 8 == 0 && row % 8 == 0) ? 1 : 0;
   p.out_vec = (uintptr_t(out) % 4 == 0 && out_stride % 2 == 0 && kv_rank % 2 == 0) ? 1 : 0;
-  const size_t smem = size_t(LA_ROWS + 2 * LA_KEYS) * (p.row_pad * 2 + 16);
   const dim3 grid((n_rows + n_entries * (p.tokens_here - 1)) / p.tokens_here, head_groups);
-  if (kv_rank <= 64) launch_latent_attention<4>(p, grid, smem, stream);
-  else if (kv_rank <= 128) launch_latent_attention<8>(p, grid, smem, stream);
-  else if (kv_rank <= 192) launch_latent_attention<12>(p, grid, smem, stream);
-  else launch_latent_attention<16>(p, grid, smem, stream);
+  if (single_rows) launch_latent_attention_of<true>(kv_rank, p, grid, stream);
+  else launch_latent_attention_of<false>(kv_rank, p, grid, stream);
   return launch_status();
 }

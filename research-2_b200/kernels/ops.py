@@ -1156,7 +1156,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         status = _lib("latent_attention").r2_latent_attention(
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), C.c_longlong(page_stride), page_size, n_pages,
             _p(block_tables), block_tables.shape[1], _p(q_start), _p(positions), _p(seq_lens), q_start.shape[0] - 1, n, n_heads,
-            head_dim, v_head_dim, C.c_float(scale), window, int(_exact_weights), _stream())
+            head_dim, v_head_dim, C.c_float(scale), window, int(_exact_weights), int(decode_only and n == q_start.shape[0] - 1), _stream())
         _check(status, "paged_attention (latents)")
         _used("latent_attention")
         return out

@@ -259,17 +259,18 @@ LATENT_SHAPES = [(12, 160, 128, 64, 16), (3, 40, 24, 0, 8), (5, 33, 20, 7, 3), (
                  (64, 24, 16, 65, 4), (2, 136, 130, 129, 128)]
 
 
-@pytest.mark.parametrize("cut", ["prompts", "decoded", "portions"])
+@pytest.mark.parametrize("cut", ["prompts", "decoded", "portions", "many"])
 @pytest.mark.parametrize("shape", LATENT_SHAPES)
 def test_attention_over_a_cache_of_latents(shape, cut):
     """The bfloat16 kernel whose tiles hold all heads of a few tokens, alone: entries of unequal lengths whose pages lie
     scattered in a pool full of large numbers, as whole prompts, as single decoded tokens and as portions that start in the
-    middle; windows that end inside, at and beyond a tile of 64 keys; rows that are no multiple of 8 or 16 numbers."""
+    middle, and as 42 entries of which every other one is a single token; windows that end inside, at and beyond a tile of 64
+    keys; rows that are no multiple of 8 or 16 numbers."""
     from research_2_b200.kernels import ops
 
     heads, row, rank, window, page = shape
     gen = torch.Generator().manual_seed(heads * 1000 + row)
-    lengths = [1, 2, 63, 64, 65, 130, 200]
+    lengths = [1, 2, 63, 64, 65, 130, 200] * (6 if cut == "many" else 1)
     scale = 1.0 / math.sqrt(row)
     per_seq = [(torch.randn(n, row, generator=gen) * 1.5).to(torch.bfloat16) for n in lengths]
     table_width = max(-(-n // page) for n in lengths)
@@ -286,6 +287,8 @@ def test_attention_over_a_cache_of_latents(shape, cut):
         spans = [(0, n) for n in lengths]
     elif cut == "decoded":
         spans = [(n - 1, n) for n in lengths]
+    elif cut == "many":
+        spans = [(n - 1, n) if e % 2 else (n // 3, n - n // 4) for e, n in enumerate(lengths)]
     else:
         spans = [(n // 3, n - n // 4) for n in lengths]
     entry_rows = [b - a for a, b in spans]
