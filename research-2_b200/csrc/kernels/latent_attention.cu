@@ -151,6 +151,8 @@ latent_prepare_kernel(T* __restrict__ buf, int row_stride, int n_heads, int q_he
 // masked in float (causal, window, context length), the softmax is online, and its weights enter the second product
 // rounded to bfloat16, or with `split_p` as the sum of two bfloat16 numbers. VT: 16-wide column tiles of the output.
 constexpr int LA_WARPS = 4, LA_ROWS = 64, LA_KEYS = 64;
+// Key tiles in flight: a decode step's CTA is alone on its SM and does little per tile, so it looks further ahead.
+constexpr int latent_stages(bool split) { return split ? 4 : 2; }
 static_assert(LA_WARPS * 32 == 2 * LA_KEYS, "the copy of a key tile gives two threads to a key");
 
 struct LatentAttnParams {
@@ -258,6 +260,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32)
 latent_attention_kernel(const LatentAttnParams p) {
   using namespace r2ptx;
   constexpr int NP = SPLIT ? 1 : LA_KEYS / 16;   // 16-key pieces of a tile that a warp takes
+  constexpr int STAGES = latent_stages(SPLIT);
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ __align__(16) uint8_t la_smem[];
@@ -332,7 +335,9 @@ latent_attention_kernel(const LatentAttnParams p) {
     const int key = tid >> 1;
     const int j = lo + it * LA_KEYS + key;
     uint8_t* dst = k_s + buf * (LA_KEYS * rs) + key * rs;
-    if (j <= hi) {
+    if (it >= n_tiles) {
+      // no such tile: an empty group keeps the count of groups in step with the tiles
+    } else if (j <= hi) {
       int page = table[page_index(j, p.page_size, p.page_shift)];
       page = (page < 0 || page >= p.n_pages) ? 0 : page;
       const bf16* src = p.cache + size_t(page) * p.page_stride + size_t(page_offset(j, p.page_size, p.page_shift)) * p.row;
@@ -370,14 +375,14 @@ latent_attention_kernel(const LatentAttnParams p) {
   const float scale2 = p.scale * 1.4426950408889634f;   // scores in units of log2(e): one exp2 per weight
   const int k_steps = p.row_pad / 16;
 
-  if (n_tiles > 0) load_keys(0, 0);
+  for (int ahead = 0; ahead < STAGES - 1; ++ahead) load_keys(ahead, ahead);
   for (int it = 0; it < n_tiles; ++it) {
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();   // tile `it` (and, the first time, the queries) is there; nobody reads the other buffer any more
-    if (it + 1 < n_tiles) load_keys(it + 1, (it + 1) & 1);
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncthreads();   // tile `it` (and, the first time, the queries) is there; nobody reads the buffer of tile `it - 1` any more
+    load_keys(it + STAGES - 1, (it + STAGES - 1) % STAGES);
     const int j0 = lo + it * LA_KEYS;
     if (!warp_has_rows || j0 + key0 > w_pmax || (p.window > 0 && j0 + key0 + 16 * NP - 1 <= w_pmin - p.window)) continue;
-    const uint32_t kt = smem_u32(k_s) + uint32_t((it & 1) * (LA_KEYS * rs));
+    const uint32_t kt = smem_u32(k_s) + uint32_t((it % STAGES) * (LA_KEYS * rs));
     float s[2 * NP][4];
 #pragma unroll
     for (int nt = 0; nt < 2 * NP; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
@@ -597,12 +602,12 @@ static inline void latent_tile_shape(int n_heads, int single_rows, int* heads_he
 
 template <int VT, bool SPLIT>
 static void launch_latent_attention(const LatentAttnParams& p, dim3 grid, cudaStream_t stream) {
-  const size_t rs = p.row_pad * 2 + 16, tiles = 2 * LA_KEYS * rs, parts = size_t(LA_WARPS) * 16 * (VT * 16 + 2) * sizeof(float);
+  const size_t rs = p.row_pad * 2 + 16, tiles = latent_stages(SPLIT) * LA_KEYS * rs, parts = size_t(LA_WARPS) * 16 * (VT * 16 + 2) * sizeof(float);
   const size_t smem = LA_ROWS * rs + (SPLIT && parts > tiles ? parts : tiles);
   static bool raised = false;   // the largest rows need more shared memory than a kernel gets unasked
   if (!raised) {
     if (cudaFuncSetAttribute(latent_attention_kernel<VT, SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (LA_ROWS + 2 * LA_KEYS) * (256 * 2 + 16)) != cudaSuccess) return;
+                             (LA_ROWS + latent_stages(SPLIT) * LA_KEYS) * (256 * 2 + 16)) != cudaSuccess) return;
     raised = true;
   }
   r2_launch(latent_attention_kernel<VT, SPLIT>, grid, dim3(LA_WARPS * 32), smem, stream, p);
