@@ -9,11 +9,15 @@
 //   r2_latent_prepare   per row of the stacked projection [q heads | c | k_rot]: RMS norm of c (statistics in float), rotation
 //                       of k_rot and of every head's rotated query part (pairs (2i, 2i + 1), angle position * freq[i], cos and
 //                       sin times `magnitude`, all in float), in place; and the row's [c | k_rot] into its cache slot. The heads'
-//                       rotated query parts are also copied to where the attention kernel reads whole query rows.
+//                       rotated query parts are also copied to where the attention kernel reads whole query rows. A further
+//                       segment of the row (a latent that the queries are made from) may be RMS-normed in the same launch;
+//                       the row may hold no query heads (they are made later, from that latent), or no latent (a second
+//                       call then rotates and copies the query parts).
 //   r2_head_linear      one small product per head: out[t][h][:] = a[t][h][:] W[h] for every head h, where the heads' vectors
 //                       lie side by side in the rows of a and out (with strides of their own) and W holds the heads' matrices
 //                       one after the other. It is what moves the keys' up-projection onto the queries and applies the
-//                       values' up-projection to the heads' weighted sums of latents.
+//                       values' up-projection to the heads' weighted sums of latents (there it may also multiply the
+//                       outputs by the sigmoid of a gate, element by element).
 //   r2_latent_attention the attention proper for bfloat16 on the warp-level tensor cores: a CTA's rows are (token, head) pairs
 //                       of one entry, so that one tile of cache rows serves all heads of several tokens.
 #include <limits.h>
@@ -33,7 +37,7 @@ constexpr int HL_ROWS = 32, HL_COLS = 64, HL_K = 32;
 template <typename T>
 __global__ void __launch_bounds__(256)
 head_linear_kernel(const T* __restrict__ a, int a_stride, int a_head, const T* __restrict__ w, int w_is_nk, T* __restrict__ out,
-                   int out_stride, int out_head, int n_rows, int k_total, int n_total) {
+                   int out_stride, int out_head, int n_rows, int k_total, int n_total, const T* __restrict__ gate, int gate_stride) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float as[HL_K][HL_ROWS + 1];
@@ -76,7 +80,11 @@ head_linear_kernel(const T* __restrict__ a, int a_stride, int a_head, const T* _
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = c0 + tx * 4 + j;
-      if (n < n_total) out[size_t(r) * out_stride + size_t(h) * out_head + n] = from_float<T>(acc[i][j]);
+      if (n < n_total) {
+        float y = acc[i][j];
+        if (gate != nullptr) y *= 1.f / (1.f + expf(-to_float(gate[size_t(r) * gate_stride + size_t(h) * out_head + n])));
+        out[size_t(r) * out_stride + size_t(h) * out_head + n] = from_float<T>(y);
+      }
     }
   }
 }
@@ -87,36 +95,50 @@ latent_prepare_kernel(T* __restrict__ buf, int row_stride, int n_heads, int q_he
                       int kv_col, int kv_rank, const float* __restrict__ norm_w, float eps, const float* __restrict__ freq,
                       float magnitude, const int32_t* __restrict__ positions, T* __restrict__ k_cache,
                       const int32_t* __restrict__ slot_mapping, int page_size, long long page_stride, int n_pages,
-                      T* __restrict__ q_out, int q_out_stride, int q_out_head_dim, int q_out_off) {
+                      T* __restrict__ q_out, int q_out_stride, int q_out_head_dim, int q_out_off, int xn_col, int xn_rank,
+                      const float* __restrict__ xn_w) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[33];
   const int t = blockIdx.x;
   T* row = buf + size_t(t) * row_stride;
   const float p = float(positions[t]);
+  if (xn_rank > 0) {   // a further normed segment: the latent that the queries are made from
+    T* x = row + xn_col;
+    float sq = 0.f;
+    for (int d = threadIdx.x; d < xn_rank; d += blockDim.x) {
+      const float v = to_float(x[d]);
+      sq = fmaf(v, v, sq);
+    }
+    const float inv = 1.f / sqrtf(block_sum(sq, scratch) / float(xn_rank) + eps);
+    for (int d = threadIdx.x; d < xn_rank; d += blockDim.x) x[d] = from_float<T>(to_float(x[d]) * inv * xn_w[d]);
+  }
+  const bool has_kv = kv_col >= 0;
   // the row's cache slot (none for a pad row, whose slot is the null page's)
   T* slot_row = nullptr;
-  if (k_cache != nullptr) {
+  if (has_kv && k_cache != nullptr) {
     const int slot = slot_mapping[t];
     const int page = slot / page_size, off = slot % page_size;
     if (slot >= 0 && page < n_pages) slot_row = k_cache + size_t(page) * page_stride + size_t(off) * (kv_rank + rot_dim);
   }
   // the latent: x / sqrt(mean(x^2) + eps) * w
-  T* c = row + kv_col;
-  float sq = 0.f;
-  for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
-    const float v = to_float(c[d]);
-    sq = fmaf(v, v, sq);
+  T* c = row + (has_kv ? kv_col : 0);
+  if (has_kv) {
+    float sq = 0.f;
+    for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
+      const float v = to_float(c[d]);
+      sq = fmaf(v, v, sq);
+    }
+    const float inv = 1.f / sqrtf(block_sum(sq, scratch) / float(kv_rank) + eps);
+    for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
+      const T y = from_float<T>(to_float(c[d]) * inv * norm_w[d]);
+      c[d] = y;
+      if (slot_row != nullptr) slot_row[d] = y;
+    }
   }
-  const float inv = 1.f / sqrtf(block_sum(sq, scratch) / float(kv_rank) + eps);
-  for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
-    const T y = from_float<T>(to_float(c[d]) * inv * norm_w[d]);
-    c[d] = y;
-    if (slot_row != nullptr) slot_row[d] = y;
-  }
-  // rotated parts: unit 0 is the shared key part, units 1 .. n_heads the heads' query parts
+  // rotated parts: unit 0 is the shared key part (where the row has one), units 1 .. n_heads the heads' query parts
   const int per_unit = rot_dim - rot_half;   // rot_half pairs, then the dimensions that pass unchanged
-  for (int idx = threadIdx.x; idx < (n_heads + 1) * per_unit; idx += blockDim.x) {
+  for (int idx = threadIdx.x + (has_kv ? 0 : per_unit); idx < (n_heads + 1) * per_unit; idx += blockDim.x) {
     const int unit = idx / per_unit, i = idx - unit * per_unit;
     T* x = unit == 0 ? c + kv_rank : row + size_t(unit - 1) * q_head_dim + q_rot_off;
     T* dst = unit == 0 ? (slot_row != nullptr ? slot_row + kv_rank : nullptr)
@@ -164,6 +186,7 @@ struct LatentAttnParams {
   int n_heads, heads_here, tokens_here;
   int row, kv_rank, row_pad;
   float scale; int window; int split_p;
+  const float* sinks;   // may be null: exp(sinks[head]) joins head's denominator (a term without key or value)
   int q_vec, k_vec, out_vec;   // 16-byte loads of queries / of cache rows, 4-byte stores of outputs are possible
 };
 
@@ -187,6 +210,7 @@ struct HeadLinearParams {
   bf16* out; int out_stride, out_head;
   int n_rows, k_total, n_total;
   int a_vec, w_vec, out_vec;   // 16-byte loads of a's / of w's rows, 4-byte stores of outputs are possible
+  const bf16* gate; int gate_stride;   // may be null: outputs times sigmoid(gate), laid out like out
 };
 
 __global__ void __launch_bounds__(128)
@@ -241,10 +265,15 @@ head_linear_mma_kernel(const HeadLinearParams p) {
     const int r = r0 + warp * 16 + g + 8 * half;
     if (r >= p.n_rows) continue;
     bf16* dst = p.out + size_t(r) * p.out_stride + size_t(h) * p.out_head;
+    const bf16* gr = p.gate != nullptr ? p.gate + size_t(r) * p.gate_stride + size_t(h) * p.out_head : nullptr;
 #pragma unroll
     for (int nt = 0; nt < HM_TILE / 8; ++nt) {
       const int n = c0 + nt * 8 + 2 * tq;
-      const float y0 = acc[nt][2 * half], y1 = acc[nt][2 * half + 1];
+      float y0 = acc[nt][2 * half], y1 = acc[nt][2 * half + 1];
+      if (gr != nullptr) {
+        if (n < p.n_total) y0 *= 1.f / (1.f + __expf(-to_float(gr[n])));
+        if (n + 1 < p.n_total) y1 *= 1.f / (1.f + __expf(-to_float(gr[n + 1])));
+      }
       if (p.out_vec && n + 1 < p.n_total) {
         *reinterpret_cast<__nv_bfloat162*>(dst + n) = __floats2bfloat162_rn(y0, y1);
       } else {
@@ -509,6 +538,7 @@ latent_attention_kernel(const LatentAttnParams p) {
           sum += theirs[VT * 16 + 1] * f;
           y += theirs[d] * f;
         }
+        if (p.sinks != nullptr) sum += exp2f(p.sinks[h0 + hh] * 1.4426950408889634f - top);
       }
       p.out[size_t(t0 + tok) * p.out_stride + size_t(h0 + hh) * p.kv_rank + d] = from_float<bf16>(sum > 0.f ? y / sum : 0.f);
     }
@@ -516,6 +546,7 @@ latent_attention_kernel(const LatentAttnParams p) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       if (tok_r[r] < 0) continue;
+      if (p.sinks != nullptr && m_run[r] != -INFINITY) l_run[r] += exp2f(p.sinks[h0 + head_r[r]] * 1.4426950408889634f - m_run[r]);
       const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
       bf16* dst = p.out + size_t(t0 + tok_r[r]) * p.out_stride + size_t(h0 + head_r[r]) * p.kv_rank;
 #pragma unroll
@@ -535,6 +566,8 @@ latent_attention_kernel(const LatentAttnParams p) {
 
 }  // namespace
 
+// (kv_col < 0: the rows hold query heads only; n_heads 0: no query heads. xn_rank > 0: the xn_rank numbers from column xn_col on are
+// RMS-normed in place with the gain xn_w and the same eps.)
 // buf [n_rows, >= kv_col + kv_rank + rot_dim] with row stride `row_stride`: n_heads query heads of q_head_dim numbers (of
 // which rot_dim from q_rot_off on are the rotated part), then at kv_col the latent (kv_rank) and the shared key part
 // (rot_dim). rot_dims (even, <= rot_dim) of the rotated parts' first dimensions turn. k_cache (may be null): rows of
@@ -544,20 +577,22 @@ extern "C" int r2_latent_prepare(void* buf, int row_stride, int n_rows, int n_he
                                  int rot_dims, int kv_col, int kv_rank, const float* norm_w, float eps, const float* freq,
                                  float magnitude, const int32_t* positions, void* k_cache, const int32_t* slot_mapping,
                                  int page_size, long long page_stride, int n_pages, void* q_out, int q_out_stride,
-                                 int q_out_head_dim, int q_out_off, int dtype, cudaStream_t stream) {
+                                 int q_out_head_dim, int q_out_off, int xn_col, int xn_rank, const float* xn_w, int dtype,
+                                 cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
-  if (n_heads < 1 || kv_rank < 1 || rot_dim < 0 || rot_dims < 0 || rot_dims % 2 != 0 || rot_dims > rot_dim ||
-      q_rot_off < 0 || q_rot_off + rot_dim > q_head_dim) return R2_BAD_SHAPE;
+  if (n_heads < 0 || (kv_col < 0 && n_heads < 1) || (kv_col >= 0 && (kv_rank < 1 || norm_w == nullptr)) || rot_dim < 0 || rot_dims < 0 ||
+      rot_dims % 2 != 0 || rot_dims > rot_dim || q_rot_off < 0 || (n_heads > 0 && q_rot_off + rot_dim > q_head_dim)) return R2_BAD_SHAPE;
+  if (xn_rank < 0 || (xn_rank > 0 && (xn_w == nullptr || xn_col < 0))) return R2_BAD_SHAPE;
   if (k_cache != nullptr && (slot_mapping == nullptr || page_size < 1)) return R2_BAD_SHAPE;
   if (q_out != nullptr && (q_out_off < 0 || q_out_off + rot_dim > q_out_head_dim)) return R2_BAD_SHAPE;
   if (dtype == R2_F32) {
     r2_launch(latent_prepare_kernel<float>, dim3(n_rows), dim3(128), size_t(0), stream, (float*)buf, row_stride, n_heads, q_head_dim,
               q_rot_off, rot_dim, rot_dims / 2, kv_col, kv_rank, norm_w, eps, freq, magnitude, positions, (float*)k_cache, slot_mapping,
-              page_size, page_stride, n_pages, (float*)q_out, q_out_stride, q_out_head_dim, q_out_off);
+              page_size, page_stride, n_pages, (float*)q_out, q_out_stride, q_out_head_dim, q_out_off, xn_col, xn_rank, xn_w);
   } else if (dtype == R2_BF16) {
     r2_launch(latent_prepare_kernel<bf16>, dim3(n_rows), dim3(128), size_t(0), stream, (bf16*)buf, row_stride, n_heads, q_head_dim,
               q_rot_off, rot_dim, rot_dims / 2, kv_col, kv_rank, norm_w, eps, freq, magnitude, positions, (bf16*)k_cache, slot_mapping,
-              page_size, page_stride, n_pages, (bf16*)q_out, q_out_stride, q_out_head_dim, q_out_off);
+              page_size, page_stride, n_pages, (bf16*)q_out, q_out_stride, q_out_head_dim, q_out_off, xn_col, xn_rank, xn_w);
   } else {
     return R2_BAD_DTYPE;
   }
@@ -566,20 +601,23 @@ extern "C" int r2_latent_prepare(void* buf, int row_stride, int n_rows, int n_he
 
 // a [n_rows, ...] with row stride a_stride, head h's k numbers at a[t][h * a_head ..]; out likewise with out_stride and out_head;
 // w: n_heads matrices of k x n numbers one after the other, each [k][n] (w_is_nk 0) or [n][k] (1).
+// gate (may be null; rows of stride gate_stride, laid out like out): out *= sigmoid(gate), element by element.
 extern "C" int r2_head_linear(const void* a, int a_stride, int a_head, const void* w, int w_is_nk, void* out, int out_stride,
-                              int out_head, int n_rows, int n_heads, int k, int n, int dtype, cudaStream_t stream) {
+                              int out_head, int n_rows, int n_heads, int k, int n, const void* gate, int gate_stride, int dtype,
+                              cudaStream_t stream) {
   if (n_rows <= 0 || n_heads <= 0 || n <= 0) return R2_OK;
   if (k < 1 || n_heads > 65535) return R2_BAD_SHAPE;
   dim3 grid((n_rows + HL_ROWS - 1) / HL_ROWS, (n + HL_COLS - 1) / HL_COLS, n_heads);
   if (dtype == R2_F32) {
     r2_launch(head_linear_kernel<float>, grid, dim3(256), size_t(0), stream, (const float*)a, a_stride, a_head, (const float*)w, w_is_nk,
-              (float*)out, out_stride, out_head, n_rows, k, n);
+              (float*)out, out_stride, out_head, n_rows, k, n, (const float*)gate, gate_stride);
   } else if (dtype == R2_BF16) {
     HeadLinearParams p;
     p.a = (const bf16*)a; p.a_stride = a_stride; p.a_head = a_head;
     p.w = (const bf16*)w; p.w_is_nk = w_is_nk;
     p.out = (bf16*)out; p.out_stride = out_stride; p.out_head = out_head;
     p.n_rows = n_rows; p.k_total = k; p.n_total = n;
+    p.gate = (const bf16*)gate; p.gate_stride = gate_stride;
     p.a_vec = (uintptr_t(a) % 16 == 0 && a_stride % 8 == 0 && a_head % 8 == 0) ? 1 : 0;
     p.w_vec = (uintptr_t(w) % 16 == 0 && (w_is_nk ? k : n) % 8 == 0 && (size_t(k) * n) % 8 == 0) ? 1 : 0;
     p.out_vec = (uintptr_t(out) % 4 == 0 && out_stride % 2 == 0 && out_head % 2 == 0) ? 1 : 0;
@@ -625,10 +663,12 @@ static void launch_latent_attention_of(int kv_rank, const LatentAttnParams& p, d
 // against the shared key part), out [n_rows, n_heads * kv_rank], cache rows of `row` numbers, page_size of them a page.
 // Entry e has the rows q_start[e] .. q_start[e + 1] - 1 at consecutive positions and its block table's row e. `single_rows`: every
 // entry is one row (a decode step); CTAs then have the heads of one token and their warps a quarter of every key tile each.
+// sinks (may be null): float [n_heads], a further term exp(sinks[h]) in head h's softmax denominator.
 extern "C" int r2_latent_attention(const void* q, int q_stride, void* out, int out_stride, const void* cache, long long page_stride,
                                    int page_size, int n_pages, const int32_t* block_tables, int table_width, const int32_t* q_start,
                                    const int32_t* positions, const int32_t* seq_lens, int n_entries, int n_rows, int n_heads, int row,
-                                   int kv_rank, float scale, int window, int split_p, int single_rows, cudaStream_t stream) {
+                                   int kv_rank, float scale, int window, int split_p, int single_rows, const float* sinks,
+                                   cudaStream_t stream) {
   if (n_rows <= 0 || n_entries <= 0) return R2_OK;
   if (single_rows && n_rows != n_entries) return R2_BAD_SHAPE;
   if (n_heads < 1 || kv_rank < 1 || kv_rank > row || row > 256 || page_size < 1 || window < 0) return R2_BAD_SHAPE;
@@ -642,7 +682,7 @@ extern "C" int r2_latent_attention(const void* q, int q_stride, void* out, int o
   latent_tile_shape(n_heads, single_rows, &p.heads_here, &p.tokens_here, &head_groups);
   p.n_heads = n_heads;
   p.row = row; p.kv_rank = kv_rank; p.row_pad = (row + 15) / 16 * 16;
-  p.scale = scale; p.window = window; p.split_p = split_p;
+  p.scale = scale; p.window = window; p.split_p = split_p; p.sinks = sinks;
   p.q_vec = (uintptr_t(q) % 16 == 0 && q_stride % 8 == 0 && row % 8 == 0) ? 1 : 0;
   p.k_vec = (uintptr_t(cache) % 16 == 0 && page_stride % 8 == 0 && row % 8 == 0) ? 1 : 0;
   p.out_vec = (uintptr_t(out) % 4 == 0 && out_stride % 2 == 0 && kv_rank % 2 == 0) ? 1 : 0;

@@ -9,7 +9,9 @@
 //   r2_route_scored   the same with sigmoid scores: an expert is chosen by its score plus a learned correction, only
 //                     inside the best groups of neighbouring experts (a group counts by its two best), and weighted by
 //                     its plain score over the chosen experts' sum; further rows of the weight matrix give sigmoid gates
-//                     of their own (one number per row of the batch, e.g. for an expert that every row uses).
+//                     of their own (one number per row of the batch, e.g. for an expert that every row uses). Or with
+//                     scores that are the softmax over all experts, groups that count by their best expert alone, and
+//                     weights that are the chosen scores times a constant (not made to sum to one).
 //   r2_expert_act     the inner activation of gated feed-forwards whose [gate | up] projections of several experts
 //                     (and of one more expert that every row uses) lie side by side in one row; each expert's
 //                     columns are multiplied by the row's weight for that expert, so that ONE down product over the
@@ -104,11 +106,14 @@ route_top_k_kernel(const T* __restrict__ h, int h_stride, const float* __restric
 // choice scores (of its one, where a group is a single expert), and only experts of the `keep` groups with the largest marks
 // can be chosen (the lower index wins a tie, among groups and among experts). The `top` largest choice scores are chosen; a
 // chosen expert's weight is its s over the sum of the chosen s (+ 1e-20).
+// softmax_scores: s = softmax of the logits over all experts instead of their sigmoids. mark_best_only: a group's mark is its
+// largest choice score alone. normalise = 0: a chosen expert's weight is s * weight_scale.
 template <typename T>
 __global__ void __launch_bounds__(256)
 route_scored_kernel(const T* __restrict__ h, int h_stride, const float* __restrict__ w, const float* __restrict__ correction,
                     float* __restrict__ dense, int32_t* __restrict__ chosen, float* __restrict__ chosen_weight,
-                    float* __restrict__ extra, int n_experts, int n_extra, int top, int n_groups, int keep, int width) {
+                    float* __restrict__ extra, int n_experts, int n_extra, int top, int n_groups, int keep, int width,
+                    int softmax_scores, int mark_best_only, int normalise, float weight_scale) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float smem[];
@@ -127,7 +132,7 @@ route_scored_kernel(const T* __restrict__ h, int h_stride, const float* __restri
     acc = warp_sum(acc);
     if (lane == 0) {
       if (n < n_experts) {
-        const float s = 1.f / (1.f + expf(-acc));
+        const float s = softmax_scores ? acc : 1.f / (1.f + expf(-acc));   // (the softmax follows once all logits are there)
         score[n] = s;
         choice[n] = s + (correction != nullptr ? correction[n] : 0.f);
       } else {
@@ -138,6 +143,26 @@ route_scored_kernel(const T* __restrict__ h, int h_stride, const float* __restri
   for (int n = threadIdx.x; n < n_experts; n += blockDim.x) dense[size_t(t) * n_experts + n] = 0.f;
   __syncthreads();
   if (warp != 0) return;
+  if (softmax_scores) {
+    // s = exp(z - max) / sum over all experts, one warp, sums in a fixed order
+    float top_z = -INFINITY;
+    for (int n = lane; n < n_experts; n += 32) top_z = fmaxf(top_z, score[n]);
+    for (int o = 16; o > 0; o >>= 1) top_z = fmaxf(top_z, __shfl_xor_sync(0xffffffffu, top_z, o));
+    float total = 0.f;
+    for (int n = lane; n < n_experts; n += 32) {
+      const float e = expf(score[n] - top_z);
+      score[n] = e;
+      total += e;
+    }
+    total = warp_sum(total);
+    const float inv_total = 1.f / total;
+    for (int n = lane; n < n_experts; n += 32) {
+      const float s = score[n] * inv_total;
+      score[n] = s;
+      choice[n] = s + (correction != nullptr ? correction[n] : 0.f);
+    }
+    __syncwarp();
+  }
   const int size = n_experts / n_groups;
   if (keep < n_groups) {
     for (int g = lane; g < n_groups; g += 32) {
@@ -147,7 +172,7 @@ route_scored_kernel(const T* __restrict__ h, int h_stride, const float* __restri
         if (c > a) { b = a; a = c; }
         else if (c > b) b = c;
       }
-      mark[g] = size > 1 ? a + b : a;
+      mark[g] = (size > 1 && !mark_best_only) ? a + b : a;
     }
     __syncwarp();
     // the kept groups: `keep` times the largest mark; a kept group's mark becomes +inf, and what is not +inf at the end is out
@@ -189,7 +214,7 @@ route_scored_kernel(const T* __restrict__ h, int h_stride, const float* __restri
     }
     __syncwarp();
   }
-  const float inv = 1.f / (sum + 1e-20f);
+  const float inv = normalise ? 1.f / (sum + 1e-20f) : weight_scale;
   for (int c = lane; c < top; c += 32) {
     const float p = chosen_weight[size_t(t) * top + c] * inv;
     chosen_weight[size_t(t) * top + c] = p;
@@ -268,10 +293,12 @@ extern "C" int r2_route_top_k(const void* h, int h_stride, const float* w, const
 }
 
 // w float [n_experts + n_extra, width]; correction float [n_experts] (may be null); dense [T, n_experts], chosen / chosen_weight
-// [T, top], extra [T, n_extra] (the further rows' logits; null when n_extra is 0).
+// [T, top], extra [T, n_extra] (the further rows' logits; null when n_extra is 0). softmax_scores, mark_best_only, normalise and
+// weight_scale choose the router's form (see the kernel).
 extern "C" int r2_route_scored(const void* h, int h_stride, const float* w, const float* correction, float* dense, int32_t* chosen,
                                float* chosen_weight, float* extra, int n_rows, int n_experts, int n_extra, int top, int n_groups,
-                               int keep, int width, int dtype, cudaStream_t stream) {
+                               int keep, int width, int softmax_scores, int mark_best_only, int normalise, float weight_scale,
+                               int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
   if (width < 1 || n_experts < 1 || n_experts > MAX_EXPERTS || top < 1 || n_groups < 1 || n_experts % n_groups != 0 || keep < 1 ||
       keep > n_groups || top > n_experts / n_groups * keep || n_extra < 0 || (n_extra > 0 && extra == nullptr)) return R2_BAD_SHAPE;
@@ -279,10 +306,10 @@ extern "C" int r2_route_scored(const void* h, int h_stride, const float* w, cons
   if (smem > 48 * 1024) return R2_UNSUPPORTED;
   if (dtype == R2_F32) {
     r2_launch(route_scored_kernel<float>, dim3(n_rows), dim3(256), smem, stream, (const float*)h, h_stride, w, correction, dense, chosen,
-              chosen_weight, extra, n_experts, n_extra, top, n_groups, keep, width);
+              chosen_weight, extra, n_experts, n_extra, top, n_groups, keep, width, softmax_scores, mark_best_only, normalise, weight_scale);
   } else if (dtype == R2_BF16) {
     r2_launch(route_scored_kernel<bf16>, dim3(n_rows), dim3(256), smem, stream, (const bf16*)h, h_stride, w, correction, dense, chosen,
-              chosen_weight, extra, n_experts, n_extra, top, n_groups, keep, width);
+              chosen_weight, extra, n_experts, n_extra, top, n_groups, keep, width, softmax_scores, mark_best_only, normalise, weight_scale);
   } else {
     return R2_BAD_DTYPE;
   }

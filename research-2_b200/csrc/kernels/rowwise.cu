@@ -684,6 +684,69 @@ rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int head_di
   }
 }
 
+// The same after an RMS norm of every head (one warp per head: the first n_q_heads heads take the gain q_w, the others k_w,
+// both of head_dim numbers; null: no norm), with cos and sin times `magnitude`: x / sqrt(mean(x^2) + eps) * w, then the
+// rotation, all in float and rounded once on the way out.
+constexpr int NORM_ROTATE_MAX_DIM = 512;
+template <typename T>
+__global__ void __launch_bounds__(128)
+norm_rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int n_q_heads, int head_dim, int half, const float* __restrict__ freq,
+                        float magnitude, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                        const int32_t* __restrict__ positions, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                        const int32_t* __restrict__ slot_mapping, int k_col, int v_col, int n_kv_heads, int v_head_dim, int page_size,
+                        long long page_stride, int n_pages) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float stage[4][NORM_ROTATE_MAX_DIM];
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const float p = float(positions[t]);
+  T* row = buf + size_t(t) * row_stride;
+  float* mine = stage[warp];
+  for (int head = warp; head < n_heads; head += 4) {
+    T* x = row + size_t(head) * head_dim;
+    const float* w = head < n_q_heads ? q_w : k_w;
+    float sq = 0.f;
+    for (int d = lane; d < head_dim; d += 32) {
+      const float v = to_float(x[d]);
+      mine[d] = v;
+      sq = fmaf(v, v, sq);
+    }
+    sq = warp_sum(sq);
+    const float inv = w != nullptr ? 1.f / sqrtf(sq / float(head_dim) + eps) : 1.f;
+    __syncwarp();
+    for (int i = lane; i < head_dim - half; i += 32) {
+      if (i < half) {
+        float sn, cs;
+        sincosf(p * freq[i], &sn, &cs);
+        sn *= magnitude;
+        cs *= magnitude;
+        const float u = mine[i] * inv * (w != nullptr ? w[i] : 1.f), v = mine[i + half] * inv * (w != nullptr ? w[i + half] : 1.f);
+        x[i] = from_float<T>(u * cs - v * sn);
+        x[i + half] = from_float<T>(v * cs + u * sn);
+      } else if (w != nullptr) {
+        const int d = i + half;   // the dimensions after the rotated ones pass with their norm alone
+        x[d] = from_float<T>(mine[d] * inv * w[d]);
+      }
+    }
+    __syncwarp();
+  }
+  if (k_cache == nullptr) return;
+  __syncthreads();
+  const int slot = slot_mapping[t];
+  const int page = slot / page_size, off = slot % page_size;
+  if (slot < 0 || page >= n_pages) return;  // never write outside the pool
+  const T* ks = row + k_col;
+  const T* vs = row + v_col;
+  for (int i = threadIdx.x; i < n_kv_heads * head_dim; i += blockDim.x) {
+    const int h = i / head_dim, d = i % head_dim;
+    k_cache[size_t(page) * page_stride + (size_t(h) * page_size + off) * head_dim + d] = ks[i];
+  }
+  for (int i = threadIdx.x; i < n_kv_heads * v_head_dim; i += blockDim.x) {
+    const int h = i / v_head_dim, d = i % v_head_dim;
+    v_cache[size_t(page) * page_stride + (size_t(h) * page_size + off) * v_head_dim + d] = vs[i];
+  }
+}
+
 // out = x + weight_sum * (a / rms(a) * wa + b / rms(b) * wb): two branches' outputs, each normalised over the row with a
 // gain of its own, join the residual stream. All float.
 __global__ void __launch_bounds__(256)
@@ -708,14 +771,34 @@ pair_norm_add_kernel(const float* __restrict__ x, const float* __restrict__ a, c
 
 // With k_cache (may be null) the launch also writes the row's keys (columns k_col .., n_kv_heads heads of head_dim, after
 // their rotation) and values (columns v_col .., heads of v_head_dim) to the row's slot of the paged cache.
+// With q_norm_w / k_norm_w (float [head_dim]; both or neither) every head is RMS-normed before its rotation: the first
+// n_q_heads heads with q_norm_w, the others with k_norm_w. `magnitude` multiplies cos and sin.
 extern "C" int r2_rotate_half(void* buf, int row_stride, int n_rows, int n_heads, int head_dim, int rot_dims, const float* inv_freq,
                               const int32_t* positions, void* k_cache, void* v_cache, const int32_t* slot_mapping, int k_col, int v_col,
-                              int n_kv_heads, int v_head_dim, int page_size, long long page_stride, int n_pages, int dtype,
+                              int n_kv_heads, int v_head_dim, int page_size, long long page_stride, int n_pages,
+                              const float* q_norm_w, const float* k_norm_w, int n_q_heads, float norm_eps, float magnitude, int dtype,
                               cudaStream_t stream) {
-  if (n_rows <= 0 || (rot_dims == 0 && k_cache == nullptr)) return R2_OK;
+  const bool normed = q_norm_w != nullptr || k_norm_w != nullptr;
+  if (n_rows <= 0 || (rot_dims == 0 && k_cache == nullptr && !normed)) return R2_OK;
   if (n_heads < 1 || rot_dims < 0 || rot_dims % 2 != 0 || rot_dims > head_dim) return R2_BAD_SHAPE;
   if (k_cache != nullptr && (v_cache == nullptr || slot_mapping == nullptr || n_kv_heads < 1 || v_head_dim < 1 || page_size < 1)) return R2_BAD_SHAPE;
   const int half = rot_dims / 2;
+  if (normed || magnitude != 1.f) {
+    if (head_dim > NORM_ROTATE_MAX_DIM || n_q_heads < 0 || n_q_heads > n_heads) return R2_BAD_SHAPE;
+    if ((n_q_heads > 0 && normed && q_norm_w == nullptr) || (n_q_heads < n_heads && normed && k_norm_w == nullptr)) return R2_BAD_SHAPE;
+    if (dtype == R2_F32) {
+      r2_launch(norm_rotate_half_kernel<float>, dim3(n_rows), dim3(128), size_t(0), stream, (float*)buf, row_stride, n_heads, n_q_heads, head_dim,
+                half, inv_freq, magnitude, q_norm_w, k_norm_w, norm_eps, positions, (float*)k_cache, (float*)v_cache, slot_mapping, k_col, v_col,
+                n_kv_heads, v_head_dim, page_size, page_stride, n_pages);
+    } else if (dtype == R2_BF16) {
+      r2_launch(norm_rotate_half_kernel<bf16>, dim3(n_rows), dim3(128), size_t(0), stream, (bf16*)buf, row_stride, n_heads, n_q_heads, head_dim,
+                half, inv_freq, magnitude, q_norm_w, k_norm_w, norm_eps, positions, (bf16*)k_cache, (bf16*)v_cache, slot_mapping, k_col, v_col,
+                n_kv_heads, v_head_dim, page_size, page_stride, n_pages);
+    } else {
+      return R2_BAD_DTYPE;
+    }
+    return launch_status();
+  }
   dim3 grid(n_rows, k_cache != nullptr ? 1 : (n_heads * half + 1023) / 1024);
   if (dtype == R2_F32) {
     r2_launch(rotate_half_kernel<float>, grid, dim3(256), size_t(0), stream, (float*)buf, row_stride, n_heads, head_dim, half, inv_freq, positions,
@@ -872,6 +955,91 @@ extern "C" int r2_xielu(const void* in, int in_stride, void* out, int out_stride
     r2_launch(xielu_kernel<float>, grid, dim3(256), size_t(0), stream, (const float*)in, in_stride, (float*)out, out_stride, width, a_pos, a_neg);
   } else if (dtype == R2_BF16) {
     r2_launch(xielu_kernel<bf16>, grid, dim3(256), size_t(0), stream, (const bf16*)in, in_stride, (bf16*)out, out_stride, width, a_pos, a_neg);
+  } else {
+    return R2_BAD_DTYPE;
+  }
+  return launch_status();
+}
+
+// ---- the norm AFTER a sum: out = (alpha x + y) / rms(alpha x + y) * w ------------------------------------------------
+// The stream's rows are scaled, a sublayer's output joins them, and the sum is normalised: all float, one CTA per row, the row
+// in registers between the passes where it fits (else the sum is made again, in the same order). `rounded` (may be null) also
+// receives the new rows in the compute dtype: what the next sublayer's products read.
+namespace {
+template <typename O>
+__global__ void __launch_bounds__(NORM_ADD_THREADS)
+add_norm_kernel(const float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ out,
+                O* __restrict__ rounded, int width, float alpha, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t at = size_t(blockIdx.x) * width;
+  const bool fits = width <= NORM_ADD_THREADS * NORM_ADD_KEEP;
+  float keep[NORM_ADD_KEEP];
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < NORM_ADD_KEEP; ++i) {
+    const int d = threadIdx.x + i * NORM_ADD_THREADS;
+    keep[i] = (fits && d < width) ? fmaf(alpha, x[at + d], y[at + d]) : 0.f;
+    sq = fmaf(keep[i], keep[i], sq);
+  }
+  if (!fits)
+    for (int d = threadIdx.x; d < width; d += NORM_ADD_THREADS) {
+      const float v = fmaf(alpha, x[at + d], y[at + d]);
+      sq = fmaf(v, v, sq);
+    }
+  const float inv = 1.f / sqrtf(block_sum(sq, scratch) / float(width) + eps);
+  if (fits) {
+#pragma unroll
+    for (int i = 0; i < NORM_ADD_KEEP; ++i) {
+      const int d = threadIdx.x + i * NORM_ADD_THREADS;
+      if (d < width) {
+        const float v = keep[i] * inv * w[d];
+        out[at + d] = v;
+        if (rounded != nullptr) rounded[at + d] = from_float<O>(v);
+      }
+    }
+  } else {
+    for (int d = threadIdx.x; d < width; d += NORM_ADD_THREADS) {
+      const float v = fmaf(alpha, x[at + d], y[at + d]) * inv * w[d];   // (out may be x: a thread reads what it alone writes)
+      out[at + d] = v;
+      if (rounded != nullptr) rounded[at + d] = from_float<O>(v);
+    }
+  }
+}
+
+template <typename O>
+__global__ void __launch_bounds__(256)
+round_rows_kernel(const float* __restrict__ x, O* __restrict__ out, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += size_t(gridDim.x) * blockDim.x) out[i] = from_float<O>(x[i]);
+}
+}  // namespace
+
+// x, y, out float [n_rows, width] (out may be x); w float [width]; rounded (may be null) [n_rows, width] in `rounded_dtype`.
+extern "C" int r2_add_norm(const float* x, const float* y, const float* w, float* out, void* rounded, int n_rows, int width,
+                           float alpha, float eps, int rounded_dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return R2_OK;
+  if (width < 1) return R2_BAD_SHAPE;
+  if (rounded == nullptr || rounded_dtype == R2_F32) {
+    r2_launch(add_norm_kernel<float>, dim3(n_rows), dim3(NORM_ADD_THREADS), size_t(0), stream, x, y, w, out, (float*)rounded, width, alpha, eps);
+  } else if (rounded_dtype == R2_BF16) {
+    r2_launch(add_norm_kernel<bf16>, dim3(n_rows), dim3(NORM_ADD_THREADS), size_t(0), stream, x, y, w, out, (bf16*)rounded, width, alpha, eps);
+  } else {
+    return R2_BAD_DTYPE;
+  }
+  return launch_status();
+}
+
+// The float rows of the stream in the compute dtype (contiguous, n numbers).
+extern "C" int r2_round_rows(const float* x, void* out, long long n, int dtype, cudaStream_t stream) {
+  if (n <= 0) return R2_OK;
+  const int blocks = int((n + 1023) / 1024 > 4096 ? 4096 : (n + 1023) / 1024);
+  if (dtype == R2_BF16) {
+    r2_launch(round_rows_kernel<bf16>, dim3(blocks), dim3(256), size_t(0), stream, x, (bf16*)out, size_t(n));
+  } else if (dtype == R2_F32) {
+    r2_launch(round_rows_kernel<float>, dim3(blocks), dim3(256), size_t(0), stream, x, (float*)out, size_t(n));
   } else {
     return R2_BAD_DTYPE;
   }

@@ -39,6 +39,8 @@ class StepContext:
         t, r, w = counts or (host.n_tokens, host.n_entries, host.n_logit_rows)
         self.n_tokens, self.n_entries, self.n_logit_rows = t, r, w
         self.captured = counts is not None
+        # (stream tensor, its rows in the compute dtype): a block whose last kernel wrote both leaves the pair here for the next one
+        self.stream_rounded = None
         # shape facts that choose kernels: inside a graph every row is an entry of its own and
         # contexts may reach the whole table; outside, the host batch says what is there
         if self.captured:

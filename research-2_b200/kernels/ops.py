@@ -554,14 +554,24 @@ def route_top_k(h: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None, top
 
 
 def rotate_half(buf: torch.Tensor, n_heads: int, head_dim: int, rot_dims: int, inv_freq: torch.Tensor, positions: torch.Tensor,
-                kv: KvScatter | None = None, n_kv_heads: int = 0, k_col: int = 0) -> None:
+                kv: KvScatter | None = None, n_kv_heads: int = 0, k_col: int = 0, *, q_norm: torch.Tensor | None = None,
+                k_norm: torch.Tensor | None = None, n_q_heads: int = 0, norm_eps: float = 0.0, magnitude: float = 1.0) -> None:
     """Rotation by position, in place, of the first `n_heads` heads of every row of `buf` (a stacked projection whose
     first columns are the query heads and then the key heads): of each head the first rot_dims dimensions, dimension i
     paired with i + rot_dims / 2, by the angle position * inv_freq[i] (float32 [rot_dims / 2]). With `kv` (see
     `kv_scatter`: `col` the first value column, `head_dim` the values' head size) the same launch puts the rotated keys
-    (n_kv_heads heads from column `k_col`) and the values into the rows' cache slots."""
+    (n_kv_heads heads from column `k_col`) and the values into the rows' cache slots. With `q_norm` / `k_norm` (float32
+    [head_dim]) every head is RMS-normed before its rotation, in float32 and in the same launch: the first `n_q_heads` heads with
+    the gain q_norm, the others with k_norm, eps `norm_eps`. `magnitude` multiplies cos and sin."""
     _need(buf, "buf", dim=2)
     _need(inv_freq, "inv_freq", torch.float32, 1)
+    for name, t in (("q_norm", q_norm), ("k_norm", k_norm)):
+        if t is not None:
+            _need(t, name, torch.float32, 1)
+            if t.shape[0] != head_dim:
+                raise KernelError(f"rotate_half: {name} {tuple(t.shape)} is not [{head_dim}]")
+    if (q_norm is not None or k_norm is not None) and ((n_q_heads > 0 and q_norm is None) or (n_q_heads < n_heads and k_norm is None)):
+        raise KernelError("rotate_half: a norm needs the gains of every kind of head that the rows hold")
     _need(positions, "positions", torch.int32, 1)
     if rot_dims % 2 or not 0 <= rot_dims <= head_dim or inv_freq.shape[0] != rot_dims // 2 or buf.shape[1] < n_heads * head_dim:
         raise KernelError(f"rotate_half: {rot_dims} of {head_dim} dimensions, {n_heads} heads in rows of {buf.shape[1]}")
@@ -570,7 +580,8 @@ def rotate_half(buf: torch.Tensor, n_heads: int, head_dim: int, rot_dims: int, i
     cache = (C.c_void_p(kv.k_cache), C.c_void_p(kv.v_cache), C.c_void_p(kv.slots), k_col, kv.col, n_kv_heads, kv.head_dim, kv.page_size,
              C.c_longlong(kv.page_stride), kv.n_pages) if kv is not None else (None, None, None, 0, 0, 0, 0, 0, C.c_longlong(0), 0)
     status = _lib("rowwise").r2_rotate_half(_p(buf), _rows(buf, "buf"), buf.shape[0], n_heads, head_dim, rot_dims, _p(inv_freq),
-                                           _p(positions), *cache, dtype_code(buf.dtype), _stream())
+                                           _p(positions), *cache, _p(q_norm), _p(k_norm), n_q_heads, C.c_float(norm_eps),
+                                           C.c_float(magnitude), dtype_code(buf.dtype), _stream())
     _check(status, "rotate_half")
 
 
@@ -617,6 +628,36 @@ def norm_add(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float,
     return out if nxt is None else (out, nxt)
 
 
+def add_norm(x: torch.Tensor, y: torch.Tensor, alpha: float, weight: torch.Tensor, eps: float, rounded_dtype: torch.dtype | None = None):
+    """(alpha x + y) / rms(alpha x + y) * weight, all float32 [T, D]: a sublayer's output joins the scaled stream and the sum is
+    normalised (the norm AFTER the sum). With `rounded_dtype` the same launch also gives the new rows in that dtype, which the
+    next sublayer's products read: -> (x_new, rounded); else -> x_new."""
+    for name, t in (("x", x), ("y", y)):
+        _need(t, name, torch.float32, 2)
+        if t.shape != x.shape or not t.is_contiguous():
+            raise KernelError(f"add_norm: {name} {tuple(t.shape)} must be contiguous and shaped like x {tuple(x.shape)}")
+    _need(weight, "weight", torch.float32, 1)
+    if weight.shape[0] != x.shape[1]:
+        raise KernelError(f"add_norm: weight {tuple(weight.shape)} does not fit the width {x.shape[1]}")
+    out = torch.empty_like(x)
+    rounded = torch.empty(x.shape, dtype=rounded_dtype, device=x.device) if rounded_dtype is not None else None
+    status = _lib("rowwise").r2_add_norm(_p(x), _p(y), _p(weight), _p(out), _p(rounded), x.shape[0], x.shape[1], C.c_float(alpha),
+                                        C.c_float(eps), dtype_code(rounded_dtype) if rounded is not None else F32, _stream())
+    _check(status, "add_norm")
+    return out if rounded is None else (out, rounded)
+
+
+def round_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 rows of the stream in the compute dtype."""
+    _need(x, "x", torch.float32, 2)
+    if not x.is_contiguous():
+        raise KernelError("round_rows: x must be contiguous")
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    status = _lib("rowwise").r2_round_rows(_p(x), _p(out), C.c_longlong(x.numel()), dtype_code(dtype), _stream())
+    _check(status, "round_rows")
+    return out
+
+
 def xielu(z: torch.Tensor, a_pos: float, a_neg: float, out: torch.Tensor | None = None) -> torch.Tensor:
     """For z > 0: a_pos z^2 + z / 2; for z <= 0: a_neg (e^z - 1 - z) + z / 2, elementwise on [T, F], computed in float32."""
     _need(z, "z", dim=2)
@@ -629,13 +670,18 @@ def xielu(z: torch.Tensor, a_pos: float, a_neg: float, out: torch.Tensor | None 
 
 
 def route_scored(h: torch.Tensor, w: torch.Tensor, correction: torch.Tensor | None, top: int, n_groups: int = 1, keep_groups: int = 1,
-                 n_extra: int = 0):
+                 n_extra: int = 0, scoring: str = "sigmoid", group_mark: str = "two_best", normalise: bool = True, weight_scale: float = 1.0):
     """Router with sigmoid scores: logits h @ w^T in float32 (w float32 [experts + n_extra, K]); an expert is chosen by
     sigmoid(logit) + correction, only inside the `keep_groups` best of `n_groups` equal groups of neighbouring experts (a
     group counts by the sum of its two largest choice scores; the lower index wins ties), the `top` largest; the chosen
     experts' weights are their sigmoids over the sum of the chosen sigmoids (+ 1e-20). The last n_extra rows of w are further
-    gates: their logits come back as they are. -> (dense float32 [T, experts]: a row's weights, zero where not chosen; chosen
+    gates: their logits come back as they are. `scoring` "softmax": the scores are the softmax of the logits over all experts
+    instead of their sigmoids. `group_mark` "best": a group counts by its largest choice score alone. `normalise` False: a chosen
+    expert's weight is its score times `weight_scale` (the weights are not made to sum to one).
+    -> (dense float32 [T, experts]: a row's weights, zero where not chosen; chosen
     int32 [T, top]; their weights float32 [T, top]; extra float32 [T, n_extra] or None)."""
+    if scoring not in ("sigmoid", "softmax") or group_mark not in ("two_best", "best"):
+        raise KernelError(f"route_scored: unknown scoring {scoring!r} or group mark {group_mark!r}")
     _need(h, "h", dim=2)
     _need(w, "w", torch.float32, 2)
     e = w.shape[0] - n_extra
@@ -652,7 +698,8 @@ def route_scored(h: torch.Tensor, w: torch.Tensor, correction: torch.Tensor | No
     weight = torch.empty(n, top, dtype=torch.float32, device=h.device)
     extra = torch.empty(n, n_extra, dtype=torch.float32, device=h.device) if n_extra else None
     status = _lib("routing").r2_route_scored(_p(h), _rows(h, "h"), _p(w), _p(correction), _p(dense), _p(chosen), _p(weight), _p(extra),
-                                            n, e, n_extra, top, n_groups, keep_groups, h.shape[1], dtype_code(h.dtype), _stream())
+                                            n, e, n_extra, top, n_groups, keep_groups, h.shape[1], int(scoring == "softmax"),
+                                            int(group_mark == "best"), int(bool(normalise)), C.c_float(weight_scale), dtype_code(h.dtype), _stream())
     _check(status, "route_scored")
     return dense, chosen, weight, extra
 
@@ -692,20 +739,30 @@ def latent_prepare(buf: torch.Tensor, n_heads: int, q_head_dim: int, q_rot_off: 
                    kv_rank: int, norm_weight: torch.Tensor, eps: float, freq: torch.Tensor, magnitude: float, positions: torch.Tensor,
                    k_cache: torch.Tensor | None = None, slot_mapping: torch.Tensor | None = None, page_size: int = 0,
                    page_stride: int = 0, n_pages: int = 0, q_out: torch.Tensor | None = None, q_out_head_dim: int = 0,
-                   q_out_off: int = 0) -> None:
+                   q_out_off: int = 0, also_norm: tuple[int, int, torch.Tensor] | None = None) -> None:
     """In place on the rows of a stacked projection [n_heads query heads of q_head_dim | latent: kv_rank | shared key part:
     rot_dim]: RMS norm of the latent (weight float32 [kv_rank], statistics in float32); rotation of the shared key part and of
     every head's last-but-`q_rot_off` part (rot_dim numbers from q_rot_off on): the first rot_dims dimensions, pairs (2i, 2i + 1),
     angle positions[t] * freq[i], cos and sin times `magnitude`. With `k_cache` the row's [latent | key part] goes to its
     cache slot (rows of kv_rank + rot_dim numbers) in the same launch. With `q_out` ([T, n_heads * q_out_head_dim]) head h's
-    rotated part is also copied to q_out[t, h, q_out_off:]."""
+    rotated part is also copied to q_out[t, h, q_out_off:]. The rows may hold no query heads (`n_heads` 0) or no latent
+    (`kv_col` < 0: query heads only, from column 0). `also_norm` (column, length, weight float32 [length]): that segment of the
+    row is RMS-normed in place too (a latent that the queries are made from), with the same eps."""
     _need(buf, "buf", dim=2)
-    _need(norm_weight, "norm_weight", torch.float32, 1)
     _need(freq, "freq", torch.float32, 1)
     _need(positions, "positions", torch.int32, 1)
-    if (buf.shape[1] < kv_col + kv_rank + rot_dim or kv_col < n_heads * q_head_dim or norm_weight.shape[0] != kv_rank
+    if kv_col >= 0:
+        _need(norm_weight, "norm_weight", torch.float32, 1)
+        if buf.shape[1] < kv_col + kv_rank + rot_dim or norm_weight.shape[0] != kv_rank:
+            raise KernelError(f"latent_prepare: rows of {buf.shape[1]} do not hold a latent of {kv_rank} and {rot_dim} more from column {kv_col} on")
+    if (buf.shape[1] < n_heads * q_head_dim or (kv_col >= 0 and kv_col < n_heads * q_head_dim) or (kv_col < 0 and n_heads < 1)
             or freq.shape[0] < rot_dims // 2 or positions.shape[0] < buf.shape[0]):
         raise KernelError(f"latent_prepare: rows of {buf.shape[1]} do not hold {n_heads} heads of {q_head_dim}, a latent of {kv_rank} and {rot_dim} more")
+    xn_col, xn_rank, xn_w = also_norm if also_norm is not None else (0, 0, None)
+    if xn_rank:
+        _need(xn_w, "also_norm weight", torch.float32, 1)
+        if xn_w.shape[0] != xn_rank or xn_col < 0 or xn_col + xn_rank > buf.shape[1]:
+            raise KernelError(f"latent_prepare: a normed segment of {xn_rank} from column {xn_col} on does not fit rows of {buf.shape[1]}")
     if k_cache is not None:
         _need(slot_mapping, "slot_mapping", torch.int32, 1)
         if k_cache.dtype != buf.dtype or slot_mapping.shape[0] < buf.shape[0]:
@@ -719,15 +776,17 @@ def latent_prepare(buf: torch.Tensor, n_heads: int, q_head_dim: int, q_rot_off: 
     status = _lib("latent_attention").r2_latent_prepare(
         _p(buf), _rows(buf, "buf"), buf.shape[0], n_heads, q_head_dim, q_rot_off, rot_dim, rot_dims, kv_col, kv_rank, _p(norm_weight),
         C.c_float(eps), _p(freq), C.c_float(magnitude), _p(positions), _p(k_cache), _p(slot_mapping), page_size,
-        C.c_longlong(page_stride), n_pages, _p(q_out), q_out_stride, q_out_head_dim, q_out_off, dtype_code(buf.dtype), _stream())
+        C.c_longlong(page_stride), n_pages, _p(q_out), q_out_stride, q_out_head_dim, q_out_off, xn_col, xn_rank, _p(xn_w),
+        dtype_code(buf.dtype), _stream())
     _check(status, "latent_prepare")
 
 
 def head_linear(a: torch.Tensor, a_head: int, w: torch.Tensor, w_is_nk: bool, out: torch.Tensor, out_head: int, n_heads: int,
-                k: int, n: int) -> torch.Tensor:
+                k: int, n: int, gate: torch.Tensor | None = None) -> torch.Tensor:
     """One small product per head: out[t, h * out_head: h * out_head + n] = a[t, h * a_head: h * a_head + k] @ W[h], float32
     sums. `w` holds the heads' matrices one after the other: [n_heads * k, n] (each [k, n]; w_is_nk False) or [n_heads * n, k]
-    (each [n, k], stored [out, in]; w_is_nk True). a and out are 2-D with contiguous rows and may be wider than the heads."""
+    (each [n, k], stored [out, in]; w_is_nk True). a and out are 2-D with contiguous rows and may be wider than the heads.
+    `gate` (laid out like out: head h's n numbers at gate[t, h * out_head:]) multiplies the outputs by its sigmoid."""
     _need(a, "a", dim=2)
     _need(w, "w", a.dtype, 2)
     _need(out, "out", a.dtype, 2)
@@ -735,8 +794,14 @@ def head_linear(a: torch.Tensor, a_head: int, w: torch.Tensor, w_is_nk: bool, ou
     if (tuple(w.shape) != want or not w.is_contiguous() or a.shape[0] != out.shape[0] or (n_heads - 1) * a_head + k > a.shape[1]
             or (n_heads - 1) * out_head + n > out.shape[1]):
         raise KernelError(f"head_linear: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit {n_heads} heads of {k} -> {n}")
+    gate_stride = 0
+    if gate is not None:
+        _need(gate, "gate", a.dtype, 2)
+        if gate.shape[0] != a.shape[0] or (n_heads - 1) * out_head + n > gate.shape[1]:
+            raise KernelError(f"head_linear: gate {tuple(gate.shape)} does not fit {n_heads} heads of {n} at a distance of {out_head}")
+        gate_stride = _rows(gate, "gate")
     status = _lib("latent_attention").r2_head_linear(_p(a), _rows(a, "a"), a_head, _p(w), int(w_is_nk), _p(out), _rows(out, "out"),
-                                                    out_head, a.shape[0], n_heads, k, n, dtype_code(a.dtype), _stream())
+                                                    out_head, a.shape[0], n_heads, k, n, _p(gate), gate_stride, dtype_code(a.dtype), _stream())
     _check(status, "head_linear")
     return out
 
@@ -1063,7 +1128,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     kernel, the mma.sync prefill kernel and the fused decode kernel.
     `values_in_keys`: the cache holds key rows only and a key's first v_head_dim numbers are its value (a cache of
     latents; `v_cache` is not read); the general kernel takes it, and for bfloat16 with one key head and `q_start` the
-    latent kernel, whose tiles hold all heads of a few tokens.
+    latent kernel, whose tiles hold all heads of a few tokens (it takes `sinks` as well).
     `decode_only` says that every row is an entry of its own (one new token each) and
     `max_context` bounds the rows' context lengths; `q_start` (int32 [R + 1]) with `n_tiles`, the
     sum over entries of ceil(rows / 64), lets the tensor-core prefill kernel take the batch. They
@@ -1150,13 +1215,14 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _used("attention_prefill")
         return out
     if (values_in_keys and n_kv_heads == 1 and q.dtype == torch.bfloat16 and _fast_attention and q_start is not None and keep_first == 0
-            and not sink and gate is None and not capped and head_dim <= 256 and v_head_dim <= head_dim):
+            and not sink and gate is None and softcap == 0.0 and head_gate is None and head_dim <= 256 and v_head_dim <= head_dim):
         # a cache of latents: every head reads the same rows, so a tile's rows are (token, head) pairs (mma.sync)
         _need(q_start, "q_start", torch.int32, 1)
         status = _lib("latent_attention").r2_latent_attention(
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), C.c_longlong(page_stride), page_size, n_pages,
             _p(block_tables), block_tables.shape[1], _p(q_start), _p(positions), _p(seq_lens), q_start.shape[0] - 1, n, n_heads,
-            head_dim, v_head_dim, C.c_float(scale), window, int(_exact_weights), int(decode_only and n == q_start.shape[0] - 1), _stream())
+            head_dim, v_head_dim, C.c_float(scale), window, int(_exact_weights), int(decode_only and n == q_start.shape[0] - 1), _p(sinks),
+            _stream())
         _check(status, "paged_attention (latents)")
         _used("latent_attention")
         return out

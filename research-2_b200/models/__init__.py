@@ -1,4 +1,4 @@
-from . import bosenex, gpt2, zirunex, zudalorn  # noqa: F401
+from . import bosenex, gpt2, pidodra, zirunex, zudalorn  # noqa: F401
 from .decoder import DecoderModel, ModelSpec, ScheduleEntry
 from .loading import load_model
 

@@ -77,7 +77,7 @@ class DecoderModel:
                 build_part("norm", layer.norm_1, tensors, rt), mixer,
                 build_part("norm", layer.norm_2, tensors, rt) if layer.norm_2 is not None else None,
                 build_part("feed_forward", layer.feed_forward, tensors, rt) if layer.feed_forward is not None else None,
-                rt.dtype, **post))
+                rt.dtype, **post, **layer.block_params))
         mixers = [b.mixer for b in self.blocks]
         self.schedule = spec.schedule or default_schedule(spec.layers, mixers)
         head_table = self.embedding.table if spec.head == spec.embedding else tensors[spec.head].to(rt.device, rt.dtype)

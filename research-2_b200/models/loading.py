@@ -9,7 +9,7 @@ import torch
 from ..config.registry import load_config
 from ..parts import Runtime
 from ..weights.loader import load_weights
-from . import bosenex, gpt2, zirunex, zudalorn  # noqa: F401  (registers the architectures)
+from . import bosenex, gpt2, pidodra, zirunex, zudalorn  # noqa: F401  (registers the architectures)
 
 DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
 

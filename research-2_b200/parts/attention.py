@@ -205,10 +205,17 @@ class RotaryWindowAttention:
         weights = exp(s) / (sum over seen keys of exp(s) + exp(sink[head]))     (the sink has no key and no value)
         head's output * sigmoid(w_gate h)[head], then w_out
 
-    params: n_heads, n_kv_heads, head_dim, v_head_dim, scale, softcap, window, rot_dims, rot_base.
+    With `qk_norm_eps` every query and key head is RMS-normed before its rotation (weights q_norm, k_norm [head_dim], plain
+    gains shared by the heads of a kind), in the rotation's launch. The rotation's frequencies are rot_base^(-2 i / rot_dims), or
+    the list `rot_freqs` (stretched ones, made by the caller), with cos and sin times `rot_magnitude`. A layer without w_k and
+    w_v has no keys and values of its own: it reads a cache member that another layer writes (keys as that layer cached
+    them, after norm and rotation) and must be scheduled with `writes_cache=False`.
+
+    params: n_heads, n_kv_heads, head_dim, v_head_dim, scale, softcap, window, rot_dims, rot_base | rot_freqs, rot_magnitude,
+    qk_norm_eps.
     weights (matrices stored [out, in], no biases): w_q [H * head_dim, D], w_k [G * head_dim, D], w_v [G * v_head_dim, D],
-    w_out [D, H * v_head_dim], and optionally sink [H], w_gate [H, D].
-    Keys are cached after their rotation. Angles, scores, softmax, sink and gate are computed in float32."""
+    w_out [D, H * v_head_dim], and optionally sink [H], w_gate [H, D], q_norm [head_dim], k_norm [head_dim].
+    Keys are cached after their rotation. Norms, angles, scores, softmax, sink and gate are computed in float32."""
 
     def __init__(self, params: dict, weights: dict, rt: Runtime):
         self.n_heads, self.n_kv_heads = int(params["n_heads"]), int(params["n_kv_heads"])
@@ -224,8 +231,10 @@ class RotaryWindowAttention:
             raise ValueError(f"attention: {self.rot_dims} rotated dimensions of a head of {self.head_dim}")
         self.q_width, self.k_width = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
         self.v_width, self.o_width = self.n_kv_heads * self.v_head_dim, self.n_heads * self.v_head_dim
-        stacked = [weights["w_q"], weights["w_k"], weights["w_v"]]
-        if [w.shape[0] for w in stacked] != [self.q_width, self.k_width, self.v_width] or weights["w_out"].shape[1] != self.o_width:
+        self.own_kv = weights.get("w_k") is not None     # else: the keys and values of another layer's cache member
+        stacked = [weights["w_q"], weights["w_k"], weights["w_v"]] if self.own_kv else [weights["w_q"]]
+        want = [self.q_width, self.k_width, self.v_width][: len(stacked)]
+        if [w.shape[0] for w in stacked] != want or weights["w_out"].shape[1] != self.o_width:
             raise ValueError(f"attention: projections of {[tuple(w.shape) for w in stacked]} and an output of "
                              f"{tuple(weights['w_out'].shape)} do not fit {self.n_heads} heads, {self.n_kv_heads} kv heads "
                              f"of {self.head_dim} (values {self.v_head_dim})")
@@ -233,10 +242,23 @@ class RotaryWindowAttention:
         self.w_out = matrix(weights["w_out"], rt)
         self.sinks = vector(weights["sink"], rt) if weights.get("sink") is not None else None
         self.w_gate = vector(weights["w_gate"], rt) if weights.get("w_gate") is not None else None   # float32: one gate per head
+        self.norm_eps = float(params["qk_norm_eps"]) if params.get("qk_norm_eps") is not None else None
+        self.q_norm = self.k_norm = None
+        if self.norm_eps is not None:
+            self.q_norm = vector(weights["q_norm"], rt)
+            self.k_norm = vector(weights["k_norm"], rt) if self.own_kv else None
+            if any(w is not None and tuple(w.shape) != (self.head_dim,) for w in (self.q_norm, self.k_norm)):
+                raise ValueError(f"attention: the query and key norms' weights must be [{self.head_dim}]")
         # the rotation's frequencies: exact in float64, then rounded once to float32
         half = self.rot_dims // 2
-        freq = torch.tensor([self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(half)], dtype=torch.float64)
-        self.inv_freq = freq.to(torch.float32).to(rt.device)
+        self.rot_magnitude = float(params.get("rot_magnitude", 1.0))
+        if params.get("rot_freqs") is not None:
+            freqs = [float(f) for f in params["rot_freqs"]]
+            if len(freqs) != half:
+                raise ValueError(f"attention: {len(freqs)} frequencies for {self.rot_dims} rotated dimensions")
+        else:
+            freqs = [self.rot_base ** (-2.0 * i / self.rot_dims) for i in range(half)]
+        self.inv_freq = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(rt.device)
 
     def matrices(self):
         return [self.w_in, self.w_out]
@@ -249,19 +271,24 @@ class RotaryWindowAttention:
     capturable = True
 
     def _inner(self, h, ctx, cache, writes_cache):
+        if writes_cache != self.own_kv:
+            raise ValueError("attention: a layer with keys and values of its own writes its cache member, one without reads another's")
         proj = ops.linear(h, self.w_in, None, w_is_nk=True)
         gate = ops.small_linear(h, self.w_gate, None) if self.w_gate is not None else None
         at = self.q_width + self.k_width
         q, k, v = proj[:, : self.q_width], proj[:, self.q_width: at], proj[:, at:]
         fused_decode = writes_cache and ctx.decode_only and self.v_head_dim == self.head_dim
+        turned = self.n_heads + (self.n_kv_heads if self.own_kv else 0)    # the heads that are normed and rotated
+        norms = dict(q_norm=self.q_norm, k_norm=self.k_norm, n_q_heads=self.n_heads, norm_eps=self.norm_eps or 0.0,
+                     magnitude=self.rot_magnitude)
         if writes_cache and not fused_decode:
             # the rotation's launch also puts the rotated keys and the values into the rows' cache slots
             scatter = ops.kv_scatter(ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride, cache.page_size,
                                      cache.n_pages, at, self.v_width, self.v_head_dim)
-            ops.rotate_half(proj, self.n_heads + self.n_kv_heads, self.head_dim, self.rot_dims, self.inv_freq, ctx.positions,
-                            kv=scatter, n_kv_heads=self.n_kv_heads, k_col=self.q_width)
-        elif self.rot_dims:
-            ops.rotate_half(proj, self.n_heads + self.n_kv_heads, self.head_dim, self.rot_dims, self.inv_freq, ctx.positions)
+            ops.rotate_half(proj, turned, self.head_dim, self.rot_dims, self.inv_freq, ctx.positions,
+                            kv=scatter, n_kv_heads=self.n_kv_heads, k_col=self.q_width, **norms)
+        elif self.rot_dims or self.q_norm is not None:
+            ops.rotate_half(proj, turned, self.head_dim, self.rot_dims, self.inv_freq, ctx.positions, **norms)
         if fused_decode:
             # one new token per row: the kernel puts the new key and value into the cache itself
             mixed = ops.decode_attention_fused(
@@ -305,9 +332,14 @@ class LatentAttention:
     v-side W_uv[n] (sum_j p_j c_j), so that every head reads the same cache rows: multi-query attention over rows of
     kv_rank + rot_dim numbers.
 
+    Each chosen by what the weights hold: the queries may pass a latent of their own, q = W_uq rms_norm(W_dq h) with the weight
+    `dq_norm` (`w_dq`, `dq_norm`, `w_uq` instead of `w_q`); a learned sink per head, exp(sink[n]) in the softmax's denominator
+    without key or value (`sink`); an output gate, the heads' outputs times sigmoid(W_g h) element by element (`w_gate`).
+
     params: n_heads, head_dim, rot_dim, v_head_dim, kv_rank, scale, window, rot_dims, rot_freqs, rot_magnitude, norm_eps.
-    weights (stored [out, in], no biases): w_q [H (head_dim + rot_dim), D], w_dkv [kv_rank + rot_dim, D], dkv_norm [kv_rank], w_uk
-    [H head_dim, kv_rank], w_uv [H v_head_dim, kv_rank], w_out [D, H v_head_dim]."""
+    weights (stored [out, in], no biases): w_q [H (head_dim + rot_dim), D] or w_dq [q_rank, D], dq_norm [q_rank], w_uq
+    [H (head_dim + rot_dim), q_rank]; w_dkv [kv_rank + rot_dim, D], dkv_norm [kv_rank], w_uk [H head_dim, kv_rank], w_uv
+    [H v_head_dim, kv_rank], w_out [D, H v_head_dim]; optionally sink [H], w_gate [H v_head_dim, D]."""
 
     def __init__(self, params: dict, weights: dict, rt: Runtime):
         self.n_heads, self.head_dim, self.rot_dim = int(params["n_heads"]), int(params["head_dim"]), int(params["rot_dim"])
@@ -319,8 +351,17 @@ class LatentAttention:
             raise ValueError(f"latent attention: {self.rot_dims} rotated dimensions of {self.rot_dim} with {len(freqs)} frequencies")
         self.q_head, self.row = self.head_dim + self.rot_dim, self.kv_rank + self.rot_dim
         H = self.n_heads
-        shapes = {"w_q": (H * self.q_head, None), "w_dkv": (self.row, None), "dkv_norm": (self.kv_rank,), "w_uk": (H * self.head_dim, self.kv_rank),
+        shapes = {"w_dkv": (self.row, None), "dkv_norm": (self.kv_rank,), "w_uk": (H * self.head_dim, self.kv_rank),
                   "w_uv": (H * self.v_head_dim, self.kv_rank), "w_out": (None, H * self.v_head_dim)}
+        self.q_rank = int(weights["w_dq"].shape[0]) if weights.get("w_dq") is not None else 0   # 0: queries straight from the input
+        if self.q_rank:
+            shapes.update({"w_dq": (self.q_rank, None), "dq_norm": (self.q_rank,), "w_uq": (H * self.q_head, self.q_rank)})
+        else:
+            shapes["w_q"] = (H * self.q_head, None)
+        if weights.get("sink") is not None:
+            shapes["sink"] = (H,)
+        if weights.get("w_gate") is not None:
+            shapes["w_gate"] = (H * self.v_head_dim, None)
         for name, want in shapes.items():
             have = tuple(weights[name].shape)
             if len(have) != len(want) or any(w is not None and w != g for w, g in zip(want, have)):
@@ -328,7 +369,14 @@ class LatentAttention:
                                  f"(values {self.v_head_dim}) over a latent of {self.kv_rank}")
         if self.row > 256:
             raise ValueError(f"latent attention: cache rows of {self.row} numbers exceed the kernels' 256")
-        self.w_in = matrix(torch.cat([weights["w_q"], weights["w_dkv"]], dim=0), rt)
+        # one product for everything that reads the layer's input: [queries or their latent | latent and key part | gate]
+        self.gated = weights.get("w_gate") is not None
+        stacked = [weights["w_dq"] if self.q_rank else weights["w_q"], weights["w_dkv"]] + ([weights["w_gate"]] if self.gated else [])
+        self.w_in = matrix(torch.cat(stacked, dim=0), rt)
+        self.kv_col = stacked[0].shape[0]
+        self.w_uq = matrix(weights["w_uq"], rt) if self.q_rank else None
+        self.dq_norm = vector(weights["dq_norm"], rt) if self.q_rank else None
+        self.sinks = vector(weights["sink"], rt) if weights.get("sink") is not None else None
         self.w_uk, self.w_uv = matrix(weights["w_uk"], rt), matrix(weights["w_uv"], rt)
         self.w_out = matrix(weights["w_out"], rt)
         self.dkv_norm = vector(weights["dkv_norm"], rt)
@@ -336,7 +384,7 @@ class LatentAttention:
         self.freqs = torch.tensor(freqs, dtype=torch.float64).to(torch.float32).to(rt.device)
 
     def matrices(self):
-        return [self.w_in, self.w_uk, self.w_uv, self.w_out]
+        return [self.w_in] + ([self.w_uq] if self.q_rank else []) + [self.w_uk, self.w_uv, self.w_out]
 
     @property
     def cache_spec(self) -> MemberSpec:
@@ -349,19 +397,31 @@ class LatentAttention:
         H, d, c = self.n_heads, self.head_dim, self.kv_rank
         proj = ops.linear(h, self.w_in, None, w_is_nk=True)
         queries = torch.empty(proj.shape[0], H * self.row, dtype=proj.dtype, device=proj.device)
-        # norm of the latent, both rotations, the cache write and the copy of the rotated query parts: one launch
-        ops.latent_prepare(proj, H, self.q_head, d, self.rot_dim, self.rot_dims, H * self.q_head, c, self.dkv_norm, self.norm_eps,
-                           self.freqs, self.rot_magnitude, ctx.positions,
-                           k_cache=cache.k if writes_cache else None, slot_mapping=ctx.slot_mapping[cache.group],
-                           page_size=cache.page_size, page_stride=cache.page_stride, n_pages=cache.n_pages,
-                           q_out=queries, q_out_head_dim=self.row, q_out_off=c)
-        ops.head_linear(proj, self.q_head, self.w_uk, False, queries, self.row, H, d, c)
+        to_cache = dict(k_cache=cache.k if writes_cache else None, slot_mapping=ctx.slot_mapping[cache.group],
+                        page_size=cache.page_size, page_stride=cache.page_stride, n_pages=cache.n_pages)
+        if self.q_rank:
+            # norms of both latents, the key part's rotation and the cache write: one launch; then the queries from their latent,
+            # and their rotated parts turned and copied
+            ops.latent_prepare(proj, 0, 0, 0, self.rot_dim, self.rot_dims, self.kv_col, c, self.dkv_norm, self.norm_eps, self.freqs,
+                               self.rot_magnitude, ctx.positions, also_norm=(0, self.q_rank, self.dq_norm), **to_cache)
+            q = ops.linear(proj[:, : self.q_rank], self.w_uq, None, w_is_nk=True)
+            ops.latent_prepare(q, H, self.q_head, d, self.rot_dim, self.rot_dims, -1, 0, None, self.norm_eps, self.freqs,
+                               self.rot_magnitude, ctx.positions, q_out=queries, q_out_head_dim=self.row, q_out_off=c)
+        else:
+            # norm of the latent, both rotations, the cache write and the copy of the rotated query parts: one launch
+            q = proj
+            ops.latent_prepare(proj, H, self.q_head, d, self.rot_dim, self.rot_dims, self.kv_col, c, self.dkv_norm, self.norm_eps,
+                               self.freqs, self.rot_magnitude, ctx.positions, q_out=queries, q_out_head_dim=self.row, q_out_off=c,
+                               **to_cache)
+        ops.head_linear(q, self.q_head, self.w_uk, False, queries, self.row, H, d, c)
         mixed = ops.paged_attention(
             queries, cache.k, cache.k, cache.page_stride, cache.page_size, cache.n_pages, ctx.block_tables[cache.group], ctx.row_entry,
             ctx.positions, ctx.seq_lens, H, 1, self.row, self.scale, self.window, decode_only=ctx.decode_only,
-            max_context=ctx.max_context, q_start=ctx.q_start, n_tiles=ctx.n_attention_tiles, v_head_dim=c, values_in_keys=True)
+            max_context=ctx.max_context, q_start=ctx.q_start, n_tiles=ctx.n_attention_tiles, v_head_dim=c, values_in_keys=True,
+            sinks=self.sinks)
         out = torch.empty(proj.shape[0], H * self.v_head_dim, dtype=proj.dtype, device=proj.device)
-        ops.head_linear(mixed, c, self.w_uv, True, out, self.v_head_dim, H, c, self.v_head_dim)
+        gate = proj[:, self.kv_col + self.row:] if self.gated else None     # the gate's columns of the input product
+        ops.head_linear(mixed, c, self.w_uv, True, out, self.v_head_dim, H, c, self.v_head_dim, gate=gate)
         return out
 
     def mix(self, h, ctx, cache=None, state=None, writes_cache: bool = True):

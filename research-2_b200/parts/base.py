@@ -73,6 +73,7 @@ class LayerSpec:
     norm_2: PartSpec | None = None  # None: an arrangement with one norm
     post_norm_1: PartSpec | None = None  # arrangements with a norm after each sublayer as well
     post_norm_2: PartSpec | None = None
+    block_params: dict = field(default_factory=dict)  # constants of the arrangement itself (a factor on the stream, ...)
 
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {

@@ -113,3 +113,51 @@ class SandwichBlock:
         x, h = ops.norm_add(x, y, self.post_norm_1.gain, self.post_norm_1.eps, self.norm_2.gain, self.norm_2.eps, self.compute_dtype)
         y = self.feed_forward.mix(h, ctx)
         return ops.norm_add(x, y, self.post_norm_2.gain, self.post_norm_2.eps)
+
+
+@register_block("post_norm")
+class PostNormBlock:
+    """The norm AFTER each sum: x <- norm_1(alpha x + mixer(x)), then x <- norm_2(alpha x + feed_forward(x)). The sublayers read
+    the stream itself (in the compute dtype) and hand over their output in float32 without it (`mix`); one launch scales the
+    stream, adds the output, normalises the sum and writes the new rows twice: in float32 (the stream) and in the compute
+    dtype (what the next sublayer's products read). The norms are RMS norms (`gain`, `eps`). A layer may have no feed-forward
+    (None; then no norm_2). `alpha` is the factor on the stream inside the sums.
+
+    The compute-dtype copy of the rows that this block returns travels to the next block in `ctx.stream_rounded` as the pair
+    (stream tensor, its copy); a block that is handed another tensor (the embedding's rows) makes the copy itself."""
+
+    def __init__(self, norm_1, mixer, norm_2, feed_forward, compute_dtype, alpha: float = 1.0):
+        if feed_forward is not None and norm_2 is None:
+            raise ValueError("a post-norm block needs a norm after every sublayer that it has")
+        for part, what in ((mixer, "mixer"), (feed_forward, "feed-forward")):
+            if part is not None and not hasattr(part, "mix"):
+                raise ValueError(f"a post-norm block's {what} must offer `mix` (its output without the stream)")
+        for norm in (norm_1, norm_2):
+            if norm is not None and not hasattr(norm, "gain"):
+                raise ValueError("a post-norm block's norms must be RMS norms")
+        self.norm_1, self.mixer, self.norm_2, self.feed_forward = norm_1, mixer, norm_2, feed_forward
+        self.compute_dtype, self.alpha = compute_dtype, float(alpha)
+        self.rounds = compute_dtype != torch.float32
+
+    def _read(self, x, ctx):
+        """The stream's rows as the sublayers' products read them."""
+        if not self.rounds:
+            return x
+        carried = getattr(ctx, "stream_rounded", None)
+        if carried is not None and carried[0] is x:
+            return carried[1]
+        return ops.round_rows(x, self.compute_dtype)
+
+    def _join(self, x, y, norm):
+        if not self.rounds:
+            x = ops.add_norm(x, y, self.alpha, norm.gain, norm.eps)
+            return x, x
+        return ops.add_norm(x, y, self.alpha, norm.gain, norm.eps, self.compute_dtype)
+
+    def forward(self, x, ctx, cache=None, state=None, writes_cache: bool = True):
+        h = self._read(x, ctx)
+        x, h = self._join(x, self.mixer.mix(h, ctx, cache, state, writes_cache), self.norm_1)
+        if self.feed_forward is not None:
+            x, h = self._join(x, self.feed_forward.mix(h, ctx), self.norm_2)
+        ctx.stream_rounded = (x, h)
+        return x

@@ -146,10 +146,13 @@ class RoutedExperts:
     among the experts of the `keep_groups` best of `n_groups` equal groups of neighbours (a group counts by the sum of its two
     largest s + correction), the `top` largest; weights are the chosen experts' s over their sum (+ 1e-20). With `activation`
     "silu" an expert is W_down (g sigmoid(g) u) without clamps. With `shared.w_sg` [1, D] the expert that every row uses is
-    multiplied by sigmoid(w_sg h), one number per row.
+    multiplied by sigmoid(w_sg h), one number per row. With `scoring` "softmax" the scores s are the softmax of the logits over
+    ALL experts, chosen inside the best groups as with "sigmoid". `group_mark` "best": a group counts by its largest score alone.
+    `normalise` false: the weights are the chosen experts' scores times `route_scale` and are not made to sum to one.
 
-    params: n_experts, top, limit, alpha, up_offset, shared_limit (None: no shared expert); scoring ("softmax_top" | "sigmoid"),
-    n_groups, keep_groups, activation ("clamped_swish" | "silu"), shared (true: a shared expert, for activations without a limit).
+    params: n_experts, top, limit, alpha, up_offset, shared_limit (None: no shared expert); scoring ("softmax_top" | "sigmoid" |
+    "softmax"), n_groups, keep_groups, group_mark ("two_best" | "best"), normalise, route_scale, activation ("clamped_swish" |
+    "silu"), shared (true: a shared expert, for activations without a limit).
     weights: router [E, D], router_b [E] or correction [E], e<i>.w_gate / e<i>.w_up [F, D], e<i>.w_down [D, F] for every expert,
     and optionally shared.w_gate / shared.w_up [Fs, D], shared.w_down [D, Fs], shared.w_sg [1, D].
 
@@ -163,9 +166,11 @@ class RoutedExperts:
         self.n_experts, self.top = int(params["n_experts"]), int(params["top"])
         self.activation = params.get("activation", "clamped_swish")
         self.scoring = params.get("scoring", "softmax_top")
-        if self.activation not in ("clamped_swish", "silu") or self.scoring not in ("softmax_top", "sigmoid"):
+        if self.activation not in ("clamped_swish", "silu") or self.scoring not in ("softmax_top", "sigmoid", "softmax"):
             raise ValueError(f"routed experts: unknown activation {self.activation!r} or scoring {self.scoring!r}")
         self.n_groups, self.keep_groups = int(params.get("n_groups", 1)), int(params.get("keep_groups", 1))
+        self.group_mark, self.normalise = params.get("group_mark", "two_best"), bool(params.get("normalise", True))
+        self.route_scale = float(params.get("route_scale", 1.0))
         clamped = self.activation == "clamped_swish"
         self.limit, self.alpha, self.up_offset = (float(params[k]) if clamped else 0.0 for k in ("limit", "alpha", "up_offset"))
         self.shared = params.get("shared_limit") is not None or bool(params.get("shared", False))
@@ -186,7 +191,7 @@ class RoutedExperts:
         # a gate on the shared expert is one more row of the router's matrix: its logit comes out of the router's launch
         self.shared_gate = self.shared and weights.get("shared.w_sg") is not None
         if self.shared_gate:
-            if self.scoring != "sigmoid" or weights["shared.w_sg"].numel() != router.shape[1]:
+            if self.scoring == "softmax_top" or weights["shared.w_sg"].numel() != router.shape[1]:
                 raise ValueError("routed experts: a gate on the shared expert needs the sigmoid router and one row of the model's width")
             router = torch.cat([router, weights["shared.w_sg"].reshape(1, -1)], dim=0)
         self.router = vector(router, rt)      # float32: the router is computed in 32-bit
@@ -198,9 +203,10 @@ class RoutedExperts:
 
     def _inner(self, h):
         gate = None
-        if self.scoring == "sigmoid":
+        if self.scoring != "softmax_top":
             route, _, _, gate = ops.route_scored(h, self.router, self.correction, self.top, self.n_groups, self.keep_groups,
-                                                 n_extra=int(self.shared_gate))
+                                                 n_extra=int(self.shared_gate), scoring=self.scoring, group_mark=self.group_mark,
+                                                 normalise=self.normalise, weight_scale=self.route_scale)
         else:
             route, _, _ = ops.route_top_k(h, self.router, self.router_b, self.top)
         return ops.expert_act(ops.linear(h, self.w_gate_up, None, w_is_nk=True), self.activation, self.limit, self.alpha,
