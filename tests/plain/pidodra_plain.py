@@ -28,6 +28,9 @@ def rms_norm(x, gain, eps):
     return unit_rms(x, eps) * gain.to(F64)
 
 
+# A test may set this to a function that disturbs the stream's rows on their way into every sublayer (and into the head):
+# how far the logits of a position move under small disturbances says how well-conditioned the position is.
+DISTURB = None
 # A test may set this to a list: every router then appends, per position, how narrowly its choice was made (the smallest
 # gap between something chosen and something not, among experts and among groups).
 MARGINS = None
@@ -104,8 +107,10 @@ def latent_attention(h, w, p, cfg, eps):
     H, d, r, dv = cfg["heads"], cfg["dim"], cfg["rot_dim"], cfg["vdim"]
     pos = list(range(T))
     freqs, mag = frequencies(cfg["rot"]) if cfg.get("rot") else ([], 1.0)
-    c_q = rms_norm(lin(w[p + "dq"], h), w[p + "dq.norm"], eps)
-    q = lin(w[p + "uq"], c_q).view(T, H, d + r)
+    if cfg.get("q_rank"):
+        q = lin(w[p + "uq"], rms_norm(lin(w[p + "dq"], h), w[p + "dq.norm"], eps)).view(T, H, d + r)
+    else:
+        q = lin(w[p + "q"], h).view(T, H, d + r)
     q_plain, q_rot = q[..., :d], rotate(q[..., d:], pos, freqs, "interleaved", mag)
     latent, k_rot = latent_keys_values(h, w, p, cfg, eps, pos)
     k_plain = lin(w[p + "uk"], latent).view(T, H, d)
@@ -123,7 +128,8 @@ def latent_attention(h, w, p, cfg, eps):
 def attention_keys_values(h, w, p, cfg, eps):
     """What a layer caches per token: keys [T, G, dim] after their norm and rotation, values [T, G, vdim]."""
     T = h.shape[0]
-    G, d, dv = cfg["kv_heads"], cfg["dim"], cfg["vdim"]
+    d = cfg["dim"]
+    G, dv = cfg.get("kv_heads", cfg["heads"]), cfg.get("vdim", d)
     freqs, mag = frequencies(cfg["rot"]) if cfg.get("rot") else ([], 1.0)
     k = rms_norm(lin(w[p + "k"], h).view(T, G, d), w[p + "k.norm"], eps)
     return rotate(k, list(range(T)), freqs, "half", mag), lin(w[p + "v"], h).view(T, G, dv)
@@ -134,17 +140,18 @@ def attention(h, w, p, cfg, eps, keys_values=None):
     i + dims / 2), ordinary softmax over every earlier position, one sigmoid gate per head. With `keys_values` the layer
     has no keys and values of its own and reads another layer's."""
     T = h.shape[0]
-    H, G, d, dv = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"]
+    H, d = cfg["heads"], cfg["dim"]
+    G, dv = cfg.get("kv_heads", H), cfg.get("vdim", d)
     freqs, mag = frequencies(cfg["rot"]) if cfg.get("rot") else ([], 1.0)
     q = rms_norm(lin(w[p + "q"], h).view(T, H, d), w[p + "q.norm"], eps)
     q = rotate(q, list(range(T)), freqs, "half", mag)
     k, v = keys_values if keys_values is not None else attention_keys_values(h, w, p, cfg, eps)
-    per = H // G
+    per = H // G                                       # query head n uses key/value head n // per
+    k_of, v_of = k.repeat_interleave(per, dim=1), v.repeat_interleave(per, dim=1)
     out = torch.zeros(T, H, dv, dtype=F64)
     for i in range(T):
-        for n in range(H):
-            s = (k[: i + 1, n // per] @ q[i, n]) * cfg["scale"]
-            out[i, n] = torch.softmax(s, dim=-1) @ v[: i + 1, n // per]
+        s = torch.einsum("jhd,hd->hj", k_of[: i + 1], q[i]) * cfg["scale"]
+        out[i] = torch.einsum("hj,jhv->hv", torch.softmax(s, dim=-1), v_of[: i + 1])
     gate = torch.sigmoid(lin(w[p + "g"], h))          # [T, H]
     return lin(w[p + "o"], (out * gate[:, :, None]).reshape(T, H * dv)), (k, v)
 
@@ -198,20 +205,24 @@ def experts(h, w, p, cfg):
 def forward(config, w, tokens, layers_out=None):
     """Logits [T, vocab] of one sequence; `layers_out` (a list) receives the stream after every layer."""
     eps, alpha = config["norm"]["eps"], float(config["postln_alpha"])
-    x = w["embed"].to(F64)[torch.tensor(tokens)] * float(config["embedding"]["scale"])
+    def read(rows):
+        return DISTURB(rows) if DISTURB is not None else rows
+
+    eps, alpha = config["norm"]["eps"], float(config.get("postln_alpha", 1.0))
+    x = w["embed"].to(F64)[torch.tensor(tokens)] * float((config.get("embedding") or {}).get("scale", 1.0))
     cached = {}
     for i, layer in enumerate(config["layers"]):
         p, m = f"l{i}.", layer["mixer"]
         if layer["type"] == "latent_attention":
-            y = latent_attention(x, w, p + "mix.", m, eps)
+            y = latent_attention(read(x), w, p + "mix.", m, eps)
         else:
-            y, cached[i] = attention(x, w, p + "mix.", m, eps, cached[m["kv_from"]] if m.get("kv_from") is not None else None)
+            y, cached[i] = attention(read(x), w, p + "mix.", m, eps, cached[m["kv_from"]] if m.get("kv_from") is not None else None)
         x = rms_norm(alpha * x + y, w[p + "norm1"], eps)
         if layer.get("mlp") is not None:
-            x = rms_norm(alpha * x + experts(x, w, p + "mlp.", layer["mlp"]), w[p + "norm2"], eps)
+            x = rms_norm(alpha * x + experts(read(x), w, p + "mlp.", layer["mlp"]), w[p + "norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
-    return lin(w["head"], rms_norm(x, w["final.norm"], eps))
+    return lin(w["head"], read(rms_norm(x, w["final.norm"], eps)))
 
 
 def read_model(folder):
