@@ -20,7 +20,8 @@ A "step" is one decode step. The default run decodes a batch of 8 requests whose
   kernels    the step's dominant kernels one by one: microseconds and fraction of the measured peak
 
 `--design bosenex` prints the same points for a Bosenex model beside a Zirunex model of equal layer sizes, and the
-design's kernels one by one; `--design zudalorn` a Zudalorn model beside a Bosenex model of equal layer sizes, likewise. `--design zirunex` prints, instead, the same decode and prefill points for Zirunex models with the layer sizes
+design's kernels one by one; `--design zudalorn` a Zudalorn model beside a Bosenex model of equal layer sizes, likewise;
+`--design pidodra` a Pidodra model beside a Zudalorn model of equal layer sizes whose layers are all latent attention. `--design zirunex` prints, instead, the same decode and prefill points for Zirunex models with the layer sizes
 of `--model` beside GPT-2's, and the design's kernels one by one beside their likes.
 
 `--model gpt2-355M` and `--model gpt2-1.5B` run the same at those sizes (the 1.5B decode workload has
@@ -283,6 +284,8 @@ def prefill_point(model, cfg, pk: dict) -> dict:
         flops = bosenex_flops(cfg, n_req, length)
     elif type(cfg).__name__ == "ZudalornConfig":
         flops = zudalorn_flops(cfg, n_req, length)
+    elif type(cfg).__name__ == "PidodraConfig":
+        flops = pidodra_flops(cfg, n_req, length)
     else:
         flops = gated_design_flops(cfg, n_req, length)
     return {"value": t / (ms / 1e3), "tokens": t, "ms": ms, "frac": flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
@@ -741,6 +744,227 @@ def zudalorn_points(args, pk: dict) -> dict:
     return out
 
 
+def pidodra_config(size: str, n_layer: int) -> dict:
+    """A Pidodra configuration with the width, heads, head size, layers and vocabulary of a GPT-2 size: of every four layers
+    two are latent attention (per head a plain part of the head size and a rotated part of half of it, a latent of two head
+    sizes, queries through a latent of half the width), one is grouped attention (about four query heads a key/value head, the
+    whole head rotated with stretched frequencies) and one is grouped attention that reads that layer's keys and values. Every
+    position sees every earlier one. Every layer routes each token to 2 of 8 experts (4 groups of which 2 are kept) of a
+    quarter of the gated width."""
+    g = SIZES[size]
+    d, h = g["n_embd"], g["n_head"]
+    hd = d // h
+    ff = max(128, round(2 * g["n_inner"] / 3 / 128) * 128)
+    latent = {"heads": h, "dim": hd, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 2 * hd, "q_rank": d // 2, "scale": (hd + hd // 2) ** -0.5,
+              "rot": {"dims": hd // 2, "base": 10000.0}}
+    scaling = {"factor": 4.0, "original": 256, "fast": 32.0, "slow": 1.0}
+    attention = {"heads": h, "kv_heads": kv_heads_for(h), "dim": hd, "vdim": hd, "scale": hd ** -0.5, "rot": {"dims": hd, "base": 10000.0, "scaling": scaling}}
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}, "scale": 2.0}, "expert": {"ff": ff // 4}}
+    layers = []
+    for i in range(n_layer):
+        if i % 2 == 0:
+            mixer, kind = latent, "latent_attention"
+        else:
+            mixer, kind = (dict(attention, kv_from=i - 2) if i % 4 == 3 else attention), "attention"
+        layers.append({"type": kind, "mixer": mixer, "mlp": moe})
+    return {"architecture": "Pidodra", "vocab": g["vocab_size"], "width": d, "norm": {"eps": 1e-5}, "embedding": {"scale": 2.0}, "postln_alpha": 2.0,
+            "layers": layers}
+
+
+def zudalorn_latent_config(size: str, n_layer: int) -> dict:
+    """The closest of the other models at equal layer sizes: a Zudalorn configuration whose layers are all latent attention
+    over every earlier position (the same heads and latent as the Pidodra configuration's), each with 2 of 8 routed experts
+    and one more for every token."""
+    data = zudalorn_config(size, n_layer)
+    latent = dict(next(layer["mixer"] for layer in data["layers"] if layer["type"] == "latent_attention"))
+    latent.pop("mask")
+    moe = next(layer["mlp"] for layer in data["layers"] if layer["mlp"]["kind"] == "moe")
+    data["layers"] = [{"type": "latent_attention", "mixer": latent, "mlp": moe} for _ in range(n_layer)]
+    return data
+
+
+def pidodra_flops(cfg, n_req: int, length: int) -> float:
+    """Flops that one prefill step of n_req prompts of `length` tokens NEEDS in a Pidodra configuration: products with the
+    weights a token uses (its chosen experts, not all) and the attention's seen pairs (over latent rows in latent layers, with
+    the keys' and values' small matrices applied on the query side, once per row and head)."""
+    from research_2_b200.config.pidodra import LatentAttentionMixer
+
+    t, d, total = n_req * length, cfg.width, 0.0
+    pairs = length * (length + 1) // 2
+    for layer in cfg.layers:
+        m = layer.mixer
+        if isinstance(m, LatentAttentionMixer):
+            row, q_width = m.kv_rank + m.rot_dim, m.heads * (m.dim + m.rot_dim)
+            total += 2 * t * (d * m.q_rank + m.q_rank * q_width if m.q_rank else d * q_width) + 2 * t * d * (row + m.heads * m.vdim)
+            total += 2 * t * m.heads * m.vdim * d + 2 * t * m.heads * m.kv_rank * (m.dim + m.vdim)
+            total += n_req * 2 * m.heads * (row + m.kv_rank) * pairs
+        else:
+            own = 0 if m.kv_from is not None else m.kv_heads * (m.dim + m.vdim)
+            total += 2 * t * d * (m.heads * m.dim + own + m.heads) + 2 * t * m.heads * m.vdim * d
+            total += n_req * 2 * m.heads * (m.dim + m.vdim) * pairs
+        if layer.mlp is not None:
+            total += 2 * t * d * (3 * layer.mlp.top * layer.mlp.ff + layer.mlp.experts)
+    return total + 2 * n_req * d * cfg.vocab_size
+
+
+def pidodra_points(args, pk: dict) -> dict:
+    """`--design pidodra`: prefill and decode throughput of a Pidodra model with the layer sizes of `--model`, beside a
+    Zudalorn model of that size whose layers are all latent attention (the closest of the other models) through the same
+    loops, and the design's kernels one by one beside their likes."""
+    import torch
+    from research_2_b200.kernels import ops
+    from research_2_b200.profiling import kernel_cases
+
+    g = SIZES[args.model]
+    d, h = g["n_embd"], g["n_head"]
+    hd = d // h
+    variants = {"zudalorn, latent attention in every layer": zudalorn_latent_config(args.model, args.layers), "pidodra": pidodra_config(args.model, args.layers)}
+    out = {"design": "pidodra", "sizes_of": args.model, "layers": args.layers, "prompt_len": PROMPT_LEN, "models": {}}
+    for name, data in variants.items():
+        model, cfg = build_gated_design(data)
+        point = {}
+        for batch in (8, 64):
+            steps = min(args.steps, 96)
+            value, ms, loop, kv_bytes = decode_point(model, batch, steps, args.warmup)
+            achieved = (model.weight_bytes_per_step() + kv_bytes) / (ms / 1e3) / 1e9
+            point[f"decode_b{batch}"] = {"tokens/s": round(value), "ms_per_step": round(ms, 4), "kernels_per_step": loop.graph.kernels,
+                                         "hbm_frac": round(achieved / pk["hbm_gbs"], 3)}
+            del loop
+            torch.cuda.empty_cache()
+        pre = prefill_point(model, cfg, pk)
+        point["prefill_2x1024"] = {"tokens/s": round(pre["value"]), "ms": round(pre["ms"], 3), "bf16_frac": round(pre["frac"], 3)}
+        out["models"][name] = point
+        del model
+        torch.cuda.empty_cache()
+
+    # the design's kernels one by one, at a prompt step (2 x 1,024 rows) and a decode step (8 rows at position 1,023)
+    table = {}
+
+    def add(name, fn, n_bytes=0, flops=0):
+        us = kernel_cases.time_in_graph(fn)
+        entry = {"us": round(us, 2)}
+        if n_bytes:
+            entry.update(frac=round(n_bytes / us / 1e3 / pk["hbm_gbs"], 3), of="copy bandwidth")
+        if flops:
+            entry.update(flops_frac=round(flops / us / 1e6 / pk["bf16_tflops"], 4))
+        table[name] = entry
+
+    dev, bf = "cuda:0", torch.bfloat16
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)  # noqa: E731
+    ff = max(128, round(2 * g["n_inner"] / 3 / 128) * 128)
+    page, length = PAGE, 1024
+    for label, n_entries, rows_each in (("2 x 1,024 rows", 2, 1024), ("8 decoded rows", 8, 1)):
+        t = n_entries * rows_each
+        q_start = i32([i * rows_each for i in range(n_entries + 1)])
+        row_entry = i32([e for e in range(n_entries) for _ in range(rows_each)])
+        positions = i32([length - 1 if rows_each == 1 else p for _ in range(n_entries) for p in range(rows_each)])
+        seq_lens = i32([length] * n_entries)
+        n_tiles = n_entries * -(-rows_each // 64)
+        pages_each = length // page
+        tables = torch.arange(n_entries * pages_each, dtype=torch.int32, device=dev).view(n_entries, pages_each).contiguous()
+        seen = sum(p + 1 for p in positions.tolist())   # (row, key) pairs: every earlier position is seen
+        keys_read = n_entries * length                  # distinct cache rows that the step reads
+        slot_map = i32([e * length + p for e, p in zip(row_entry.tolist(), positions.tolist())])
+        x32, y32 = torch.randn(t, d, device=dev), torch.randn(t, d, device=dev)
+        hrow = torch.randn(t, d, device=dev).to(bf)
+        gain = torch.ones(d, device=dev)
+        add(f"the norm after a sum: scaled stream + a sublayer's output, normed, in float32 and bfloat16, {label}",
+            lambda: ops.add_norm(x32, y32, 2.0, gain, 1e-5, bf), n_bytes=t * d * 14)
+        add(f"its like: a sublayer's output normed into the stream + the next norm (Zudalorn), {label}",
+            lambda: ops.norm_add(x32, y32, gain, 1e-5, gain, 1e-5, bf), n_bytes=t * d * 14)
+        # latent attention: the launches around the queries' up-projection, the small products per head, the attention
+        c, r, q_rank = 2 * hd, hd // 2, d // 2
+        row, q_head = c + r, hd + r
+        proj = torch.randn(t, q_rank + row + h * hd, device=dev).to(bf)
+        q = torch.randn(t, h * q_head, device=dev).to(bf)
+        queries = torch.randn(t, h * row, device=dev).to(bf)
+        lat_cache = torch.randn(n_entries * pages_each, page * row, device=dev).to(bf)
+        norm_w, norm_q = torch.ones(c, device=dev), torch.ones(q_rank, device=dev)
+        freq = torch.tensor([10000.0 ** (-2.0 * i / r) for i in range(r // 2)], device=dev)
+        add(f"latent attention: both latents' norms, the key part's rotation, cache row, {label}",
+            lambda: ops.latent_prepare(proj, 0, 0, 0, r, r, q_rank, c, norm_w, 1e-5, freq, 1.0, positions, k_cache=lat_cache.view(-1),
+                                       slot_mapping=slot_map, page_size=page, page_stride=page * row, n_pages=lat_cache.shape[0],
+                                       also_norm=(0, q_rank, norm_q)), n_bytes=t * ((q_rank + row) * 4 + row * 2))
+        add(f"latent attention: the heads' rotated query parts turned and copied, {label}",
+            lambda: ops.latent_prepare(q, h, q_head, hd, r, r, -1, 0, None, 1e-5, freq, 1.0, positions, q_out=queries, q_out_head_dim=row, q_out_off=c),
+            n_bytes=t * h * r * 6)
+        zq = torch.randn(t, h * q_head + row, device=dev).to(bf)
+        add(f"their like: latent's norm, rotations, cache row in one launch (Zudalorn), {label}",
+            lambda: ops.latent_prepare(zq, h, q_head, hd, r, r, h * q_head, c, norm_w, 1e-5, freq, 1.1, positions, k_cache=lat_cache.view(-1),
+                                       slot_mapping=slot_map, page_size=page, page_stride=page * row, n_pages=lat_cache.shape[0], q_out=queries,
+                                       q_out_head_dim=row, q_out_off=c), n_bytes=t * (h * r * 6 + row * 6))
+        mixed = torch.empty(t, h * c, device=dev, dtype=bf)
+        sinks = torch.randn(h, device=dev)
+        attend = lambda s: ops.paged_attention(queries, lat_cache.view(-1), lat_cache.view(-1), page * row, page, lat_cache.shape[0], tables,  # noqa: E731
+                                               row_entry, positions, seq_lens, h, 1, row, 0.1, 0, out=mixed, decode_only=rows_each == 1,
+                                               max_context=length, q_start=q_start, n_tiles=n_tiles, v_head_dim=c, values_in_keys=True, sinks=s)
+        att = dict(n_bytes=t * h * (row + c) * 2 + keys_read * row * 2, flops=2 * seen * h * (row + c))
+        add(f"latent attention over rows of {row} with sinks, {h} heads, every earlier key, {label}", lambda: attend(sinks), **att)
+        add(f"its like: the same without sinks (Zudalorn), {label}", lambda: attend(None), **att)
+        w_uv = torch.randn(h * hd, c, device=dev).to(bf)
+        heads_out = torch.empty(t, h * hd, device=dev, dtype=bf)
+        gate = proj[:, q_rank + row:]
+        add(f"latent attention: values' matrices after the sums with the output gate, {h} heads of {c} -> {hd}, {label}",
+            lambda: ops.head_linear(mixed, c, w_uv, True, heads_out, hd, h, c, hd, gate=gate), n_bytes=t * h * (2 * hd + c) * 2 + w_uv.numel() * 2,
+            flops=2 * t * h * hd * c)
+        add(f"its like: the same without a gate (Zudalorn), {label}",
+            lambda: ops.head_linear(mixed, c, w_uv, True, heads_out, hd, h, c, hd), n_bytes=t * h * (hd + c) * 2 + w_uv.numel() * 2, flops=2 * t * h * hd * c)
+        # grouped attention: norms and rotation in one launch, the attention with one gate per head
+        kvh = kv_heads_for(h)
+        qkv = torch.randn(t, (h + 2 * kvh) * hd, device=dev).to(bf)
+        kv_pool = torch.randn(n_entries * pages_each, 2 * kvh * page * hd, device=dev).to(bf).view(-1)
+        inv_freq = torch.tensor([10000.0 ** (-2.0 * i / hd) for i in range(hd // 2)], device=dev)
+        head_w = torch.ones(hd, device=dev)
+        scatter = ops.kv_scatter(slot_map, kv_pool, kv_pool[kvh * page * hd:], 2 * kvh * page * hd, page, n_entries * pages_each, (h + kvh) * hd, kvh * hd, hd)
+        add(f"attention: heads' norms, rotation and cache write in one launch, {h} + {kvh} heads of {hd}, {label}",
+            lambda: ops.rotate_half(qkv, h + kvh, hd, hd, inv_freq, positions, kv=scatter, n_kv_heads=kvh, k_col=h * hd, q_norm=head_w, k_norm=head_w,
+                                    n_q_heads=h, norm_eps=1e-5, magnitude=1.1), n_bytes=t * ((h + kvh) * hd * 4 + 2 * kvh * hd * 4))
+        add(f"its like: rotation and cache write (Bosenex), {label}",
+            lambda: ops.rotate_half(qkv, h + kvh, hd, hd, inv_freq, positions, kv=scatter, n_kv_heads=kvh, k_col=h * hd),
+            n_bytes=t * ((h + kvh) * hd * 4 + 2 * kvh * hd * 4))
+        add(f"its like: heads' norms and cache write (Zirunex), {label}",
+            lambda: ops.head_norm(qkv, h, kvh, hd, head_w, head_w, 1e-5, kv=scatter), n_bytes=t * ((h + kvh) * hd * 4 + 2 * kvh * hd * 4))
+        att_out = torch.empty(t, h * hd, device=dev, dtype=bf)
+        head_gate = torch.randn(t, h, device=dev)
+        grouped = lambda **kw: ops.paged_attention(qkv[:, : h * hd], kv_pool, kv_pool[kvh * page * hd:], 2 * kvh * page * hd, page, n_entries * pages_each,  # noqa: E731
+                                                   tables, row_entry, positions, seq_lens, h, kvh, hd, hd ** -0.5, 0, out=att_out, decode_only=rows_each == 1,
+                                                   max_context=length, q_start=q_start, n_tiles=n_tiles, **kw)
+        gqa = dict(n_bytes=t * h * hd * 4 + keys_read * 2 * kvh * hd * 2, flops=2 * seen * h * 2 * hd)
+        if rows_each > 1:
+            add(f"attention, {h} heads of {hd} over {kvh} kv heads, one gate per head, every earlier key, {label}", lambda: grouped(head_gate=head_gate), **gqa)
+            add(f"its like: the same with capped scores and sinks (Bosenex), {label}", lambda: grouped(softcap=30.0, sinks=sinks), **gqa)
+        else:
+            fused = lambda **kw: ops.decode_attention_fused(  # noqa: E731
+                qkv[:, : h * hd], qkv[:, h * hd: (h + kvh) * hd], qkv[:, (h + kvh) * hd:], slot_map, kv_pool, kv_pool[kvh * page * hd:], 2 * kvh * page * hd, page,
+                n_entries * pages_each, tables, row_entry, positions, seq_lens, h, kvh, hd, hd ** -0.5, 0, length, exact_weights=ops.exact_weights(), **kw)
+            add(f"attention with the new key's cache write in the kernel, one gate per head, {label}", lambda: fused(head_gate=head_gate), **gqa)
+            add(f"its like: the same with capped scores and sinks (Bosenex), {label}", lambda: fused(softcap=30.0, sinks=sinks), **gqa)
+            add(f"attention of a layer that reads another's keys (nothing to write), one gate per head, {label}",
+                lambda: ops.decode_attention_fused(qkv[:, : h * hd], None, None, None, kv_pool, kv_pool[kvh * page * hd:], 2 * kvh * page * hd, page,
+                                                   n_entries * pages_each, tables, row_entry, positions, seq_lens, h, kvh, hd, hd ** -0.5, 0, length,
+                                                   exact_weights=ops.exact_weights(), head_gate=head_gate), **gqa)
+        w_gate = torch.randn(h, d, device=dev) * 0.02
+        add(f"attention: one gate per head in 32-bit, {h} outputs, {label}", lambda: ops.small_linear(hrow, w_gate, None), n_bytes=t * d * 2)
+        # the mixture
+        router8 = torch.randn(8, d, device=dev) * 0.02
+        add(f"router: softmax over 8 experts in 32-bit, 2 of 4 groups by their best, top 2, scaled, {label}",
+            lambda: ops.route_scored(hrow, router8, None, 2, 4, 2, scoring="softmax", group_mark="best", normalise=False, weight_scale=2.0), n_bytes=t * d * 2)
+        router9 = torch.randn(9, d, device=dev) * 0.02
+        correction = torch.randn(8, device=dev) * 0.1
+        add(f"its like: 8 sigmoid scores + the shared expert's gate, 2 of 4 groups, top 2 (Zudalorn), {label}",
+            lambda: ops.route_scored(hrow, router9, correction, 2, 4, 2, n_extra=1), n_bytes=t * d * 2)
+        route, _, _, _ = ops.route_scored(hrow, router8, None, 2, 4, 2, scoring="softmax", group_mark="best", normalise=False, weight_scale=2.0)
+        gu = torch.randn(t, 2 * 8 * (ff // 4), device=dev).to(bf)
+        add(f"experts' gated silu unit with routing weights, {gu.shape[1] // 2:,} columns, {label}",
+            lambda: ops.expert_act(gu, "silu", route=route, n_experts=8, expert_width=ff // 4), n_bytes=t * gu.shape[1] * 3)
+        route2, _, _, sg = ops.route_scored(hrow, router9, correction, 2, 4, 2, n_extra=1)
+        gu2 = torch.randn(t, 2 * 9 * (ff // 4), device=dev).to(bf)
+        add(f"its like: the same with the shared expert's columns and gate (Zudalorn), {gu2.shape[1] // 2:,} columns, {label}",
+            lambda: ops.expert_act(gu2, "silu", route=route2, n_experts=8, expert_width=ff // 4, tail_gate=sg), n_bytes=t * gu2.shape[1] * 3)
+    out["kernels"] = table
+    return out
+
+
 def e2e_point(model, batch: int, steps: int, warmup: int) -> dict:
     """Through the Python entry point: submit prompts (host token lists), step, poll tokens."""
     import torch
@@ -914,7 +1138,7 @@ def main() -> int:
     ap.add_argument("--phases", action="store_true", help="print where a layer's time goes inside the resident decode kernel at --batch rows, and stop")
     ap.add_argument("--logits-ctas", action="store_true", help="print when each CTA of a decode step's logits product starts and ends (its waves), and stop")
     ap.add_argument("--prefill", action="store_true", help="print the prefill point (2 x 1,024 tokens in one step) alone, and stop")
-    ap.add_argument("--design", default=None, choices=("zirunex", "bosenex", "zudalorn"),
+    ap.add_argument("--design", default=None, choices=("zirunex", "bosenex", "zudalorn", "pidodra"),
                     help="print prefill and decode throughput of that design at the layer sizes of --model beside GPT-2's, "
                          "and its kernels beside their likes, and stop (the default workload is GPT-2's)")
     args = ap.parse_args()
@@ -949,7 +1173,7 @@ def main() -> int:
 
     pk, pk_source = peaks()
     if args.design:
-        points = {"bosenex": bosenex_points, "zudalorn": zudalorn_points}.get(args.design, design_points)
+        points = {"bosenex": bosenex_points, "zudalorn": zudalorn_points, "pidodra": pidodra_points}.get(args.design, design_points)
         print(json.dumps(points(args, pk)))
         return 0
     model, cfg = build_model(args.layers, size=args.model)

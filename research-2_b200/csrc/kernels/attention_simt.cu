@@ -19,9 +19,9 @@
 namespace {
 
 constexpr int WARPS = 4;
-constexpr int MAX_HEAD_DIM = 256;
+constexpr int WIDE_HEAD_DIM = 1024;   // a second instance takes rows of up to this many numbers (a cache of long latents)
 
-template <typename T>
+template <typename T, int MAX_HEAD_DIM>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, int q_row_stride, T* __restrict__ out, int out_row_stride,
                       const T* __restrict__ k_cache, const T* __restrict__ v_cache, long long page_stride,
@@ -137,18 +137,27 @@ extern "C" int r2_attention_simt(const void* q, int q_row_stride, void* out, int
                                  float softcap, const float* sinks, const float* head_gate, int head_gate_stride,
                                  int v_row_stride, cudaStream_t stream) {
   if (n_rows <= 0) return R2_OK;
-  if (head_dim < 1 || head_dim > MAX_HEAD_DIM || v_head_dim < 1 || v_head_dim > MAX_HEAD_DIM) return R2_UNSUPPORTED;
+  if (head_dim < 1 || head_dim > WIDE_HEAD_DIM || v_head_dim < 1 || v_head_dim > WIDE_HEAD_DIM) return R2_UNSUPPORTED;
+  const bool wide = head_dim > 256 || v_head_dim > 256;
   if (n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || page_size < 1 || window < 0 || keep_first < 0) return R2_BAD_SHAPE;
   if (v_row_stride <= 0) v_row_stride = v_head_dim;   // values in rows of their own
   if (v_row_stride < v_head_dim) return R2_BAD_SHAPE;
   dim3 grid(n_rows, (n_heads + WARPS - 1) / WARPS);
   if (dtype == R2_F32) {
-    r2_launch(attention_simt_kernel<float>, dim3(grid), dim3(WARPS * 32), size_t(0), stream,
+    if (wide) r2_launch(attention_simt_kernel<float, WIDE_HEAD_DIM>, dim3(grid), dim3(WARPS * 32), size_t(0), stream,
+        (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_cache, (const float*)v_cache,
+        page_stride, page_size, block_tables, table_width, row_entry, positions, seq_lens, n_heads, n_kv_heads,
+        head_dim, v_head_dim, scale, window, keep_first, sink, (const float*)gate, gate_row_stride, n_pages, softcap, sinks, head_gate, head_gate_stride, v_row_stride);
+    else r2_launch(attention_simt_kernel<float, 256>, dim3(grid), dim3(WARPS * 32), size_t(0), stream,
         (const float*)q, q_row_stride, (float*)out, out_row_stride, (const float*)k_cache, (const float*)v_cache,
         page_stride, page_size, block_tables, table_width, row_entry, positions, seq_lens, n_heads, n_kv_heads,
         head_dim, v_head_dim, scale, window, keep_first, sink, (const float*)gate, gate_row_stride, n_pages, softcap, sinks, head_gate, head_gate_stride, v_row_stride);
   } else if (dtype == R2_BF16) {
-    r2_launch(attention_simt_kernel<bf16>, dim3(grid), dim3(WARPS * 32), size_t(0), stream,
+    if (wide) r2_launch(attention_simt_kernel<bf16, WIDE_HEAD_DIM>, dim3(grid), dim3(WARPS * 32), size_t(0), stream,
+        (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_cache, (const bf16*)v_cache,
+        page_stride, page_size, block_tables, table_width, row_entry, positions, seq_lens, n_heads, n_kv_heads,
+        head_dim, v_head_dim, scale, window, keep_first, sink, (const bf16*)gate, gate_row_stride, n_pages, softcap, sinks, head_gate, head_gate_stride, v_row_stride);
+    else r2_launch(attention_simt_kernel<bf16, 256>, dim3(grid), dim3(WARPS * 32), size_t(0), stream,
         (const bf16*)q, q_row_stride, (bf16*)out, out_row_stride, (const bf16*)k_cache, (const bf16*)v_cache,
         page_stride, page_size, block_tables, table_width, row_entry, positions, seq_lens, n_heads, n_kv_heads,
         head_dim, v_head_dim, scale, window, keep_first, sink, (const bf16*)gate, gate_row_stride, n_pages, softcap, sinks, head_gate, head_gate_stride, v_row_stride);

@@ -187,6 +187,7 @@ struct LatentAttnParams {
   int row, kv_rank, row_pad;
   float scale; int window; int split_p;
   const float* sinks;   // may be null: exp(sinks[head]) joins head's denominator (a term without key or value)
+  int n_slices; float* parts;   // decode steps: a token's key tiles cut over n_slices CTAs (grid z) that leave partial sums in `parts`
   int q_vec, k_vec, out_vec;   // 16-byte loads of queries / of cache rows, 4-byte stores of outputs are possible
 };
 
@@ -210,7 +211,7 @@ struct HeadLinearParams {
   bf16* out; int out_stride, out_head;
   int n_rows, k_total, n_total;
   int a_vec, w_vec, out_vec;   // 16-byte loads of a's / of w's rows, 4-byte stores of outputs are possible
-  const bf16* gate; int gate_stride;   // may be null: outputs times sigmoid(gate), laid out like out
+  const bf16* gate; int gate_stride, gate_vec;   // may be null: outputs times sigmoid(gate), laid out like out (4-byte loads possible)
 };
 
 __global__ void __launch_bounds__(128)
@@ -271,8 +272,14 @@ head_linear_mma_kernel(const HeadLinearParams p) {
       const int n = c0 + nt * 8 + 2 * tq;
       float y0 = acc[nt][2 * half], y1 = acc[nt][2 * half + 1];
       if (gr != nullptr) {
-        if (n < p.n_total) y0 *= 1.f / (1.f + __expf(-to_float(gr[n])));
-        if (n + 1 < p.n_total) y1 *= 1.f / (1.f + __expf(-to_float(gr[n + 1])));
+        if (p.gate_vec && n + 1 < p.n_total) {
+          const float2 z = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(gr + n));
+          y0 *= 1.f / (1.f + __expf(-z.x));
+          y1 *= 1.f / (1.f + __expf(-z.y));
+        } else {
+          if (n < p.n_total) y0 *= 1.f / (1.f + __expf(-to_float(gr[n])));
+          if (n + 1 < p.n_total) y1 *= 1.f / (1.f + __expf(-to_float(gr[n + 1])));
+        }
       }
       if (p.out_vec && n + 1 < p.n_total) {
         *reinterpret_cast<__nv_bfloat162*>(dst + n) = __floats2bfloat162_rn(y0, y1);
@@ -345,8 +352,13 @@ latent_attention_kernel(const LatentAttnParams p) {
   const int seq_len = p.seq_lens[e];
   const int p_first = p.positions[t0], p_last = p.positions[t0 + n_tok - 1];
   const int hi = min(p_last, seq_len - 1);                              // newest key that any row sees
-  const int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;     // oldest
-  const int n_tiles = hi >= lo ? (hi - lo) / LA_KEYS + 1 : 0;
+  int lo = p.window > 0 ? max(0, p_first - p.window + 1) : 0;           // oldest
+  int n_tiles = hi >= lo ? (hi - lo) / LA_KEYS + 1 : 0;
+  if (SPLIT && p.n_slices > 1) {   // this CTA's share of the token's key tiles: an even cut of the tiles that the token has
+    const int per = (n_tiles + p.n_slices - 1) / p.n_slices, first = int(blockIdx.z) * per;
+    lo += first * LA_KEYS;
+    n_tiles = max(0, min(per, n_tiles - first));
+  }
   const int32_t* table = p.block_tables + size_t(e) * p.table_width;
   const int chunks = p.row_pad / 8;
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
@@ -538,8 +550,14 @@ latent_attention_kernel(const LatentAttnParams p) {
           sum += theirs[VT * 16 + 1] * f;
           y += theirs[d] * f;
         }
-        if (p.sinks != nullptr) sum += exp2f(p.sinks[h0 + hh] * 1.4426950408889634f - top);
       }
+      if (p.n_slices > 1) {   // the slices of a token meet in the merge kernel: sums relative to this slice's maximum
+        float* mine = p.parts + ((size_t(e) * p.n_heads + h0 + hh) * p.n_slices + blockIdx.z) * (p.kv_rank + 2);
+        mine[d] = y;
+        if (d == 0) { mine[p.kv_rank] = top; mine[p.kv_rank + 1] = sum; }
+        continue;
+      }
+      if (top != -INFINITY && p.sinks != nullptr) sum += exp2f(p.sinks[h0 + hh] * 1.4426950408889634f - top);
       p.out[size_t(t0 + tok) * p.out_stride + size_t(h0 + hh) * p.kv_rank + d] = from_float<bf16>(sum > 0.f ? y / sum : 0.f);
     }
   } else {
@@ -561,6 +579,38 @@ latent_attention_kernel(const LatentAttnParams p) {
         }
       }
     }
+  }
+}
+
+// A decode step's slices of one (token, head) meet: out = sum_s y_s 2^(top_s - top) / (sum_s l_s 2^(top_s - top) + the sink's term).
+// One CTA per (token, head); the slices are added in their order.
+__global__ void __launch_bounds__(128)
+latent_merge_kernel(const float* __restrict__ parts, int n_slices, int kv_rank, int n_heads, const float* __restrict__ sinks,
+                    bf16* __restrict__ out, int out_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = blockIdx.x / n_heads, h = blockIdx.x - e * n_heads;
+  const float* mine = parts + size_t(blockIdx.x) * n_slices * (kv_rank + 2);
+  float top = -INFINITY;
+  for (int s = 0; s < n_slices; ++s) top = fmaxf(top, mine[s * (kv_rank + 2) + kv_rank]);
+  float sum = 0.f;
+  if (top != -INFINITY) {
+    for (int s = 0; s < n_slices; ++s) {
+      const float t = mine[s * (kv_rank + 2) + kv_rank];
+      if (t != -INFINITY) sum += mine[s * (kv_rank + 2) + kv_rank + 1] * exp2f(t - top);
+    }
+    if (sinks != nullptr) sum += exp2f(sinks[h] * 1.4426950408889634f - top);
+  }
+  const float inv = sum > 0.f ? 1.f / sum : 0.f;
+  for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
+    float y = 0.f;
+    if (top != -INFINITY) {
+      for (int s = 0; s < n_slices; ++s) {
+        const float t = mine[s * (kv_rank + 2) + kv_rank];
+        if (t != -INFINITY) y += mine[s * (kv_rank + 2) + d] * exp2f(t - top);
+      }
+    }
+    out[size_t(e) * out_stride + size_t(h) * kv_rank + d] = from_float<bf16>(y * inv);
   }
 }
 
@@ -618,6 +668,7 @@ extern "C" int r2_head_linear(const void* a, int a_stride, int a_head, const voi
     p.out = (bf16*)out; p.out_stride = out_stride; p.out_head = out_head;
     p.n_rows = n_rows; p.k_total = k; p.n_total = n;
     p.gate = (const bf16*)gate; p.gate_stride = gate_stride;
+    p.gate_vec = (gate != nullptr && uintptr_t(gate) % 4 == 0 && gate_stride % 2 == 0 && out_head % 2 == 0) ? 1 : 0;
     p.a_vec = (uintptr_t(a) % 16 == 0 && a_stride % 8 == 0 && a_head % 8 == 0) ? 1 : 0;
     p.w_vec = (uintptr_t(w) % 16 == 0 && (w_is_nk ? k : n) % 8 == 0 && (size_t(k) * n) % 8 == 0) ? 1 : 0;
     p.out_vec = (uintptr_t(out) % 4 == 0 && out_stride % 2 == 0 && out_head % 2 == 0) ? 1 : 0;
@@ -664,11 +715,13 @@ static void launch_latent_attention_of(int kv_rank, const LatentAttnParams& p, d
 // Entry e has the rows q_start[e] .. q_start[e + 1] - 1 at consecutive positions and its block table's row e. `single_rows`: every
 // entry is one row (a decode step); CTAs then have the heads of one token and their warps a quarter of every key tile each.
 // sinks (may be null): float [n_heads], a further term exp(sinks[h]) in head h's softmax denominator.
+// n_slices > 1 (decode steps only): every token's key tiles are cut over that many CTAs, whose partial sums (in `parts`, room for
+// parts_floats floats: n_entries * n_heads * n_slices * (kv_rank + 2) are needed, else one CTA takes all) a second launch merges.
 extern "C" int r2_latent_attention(const void* q, int q_stride, void* out, int out_stride, const void* cache, long long page_stride,
                                    int page_size, int n_pages, const int32_t* block_tables, int table_width, const int32_t* q_start,
                                    const int32_t* positions, const int32_t* seq_lens, int n_entries, int n_rows, int n_heads, int row,
                                    int kv_rank, float scale, int window, int split_p, int single_rows, const float* sinks,
-                                   cudaStream_t stream) {
+                                   int n_slices, float* parts, long long parts_floats, cudaStream_t stream) {
   if (n_rows <= 0 || n_entries <= 0) return R2_OK;
   if (single_rows && n_rows != n_entries) return R2_BAD_SHAPE;
   if (n_heads < 1 || kv_rank < 1 || kv_rank > row || row > 256 || page_size < 1 || window < 0) return R2_BAD_SHAPE;
@@ -683,11 +736,20 @@ extern "C" int r2_latent_attention(const void* q, int q_stride, void* out, int o
   p.n_heads = n_heads;
   p.row = row; p.kv_rank = kv_rank; p.row_pad = (row + 15) / 16 * 16;
   p.scale = scale; p.window = window; p.split_p = split_p; p.sinks = sinks;
+  // a decode step's tokens may have their key tiles cut over several CTAs, which leave partial sums for a merge kernel
+  if (!single_rows || n_slices < 2 || parts == nullptr || (long long)n_entries * n_heads * n_slices * (kv_rank + 2) > parts_floats) n_slices = 1;
+  p.n_slices = n_slices; p.parts = parts;
   p.q_vec = (uintptr_t(q) % 16 == 0 && q_stride % 8 == 0 && row % 8 == 0) ? 1 : 0;
   p.k_vec = (uintptr_t(cache) % 16 == 0 && page_stride % 8 == 0 && row % 8 == 0) ? 1 : 0;
   p.out_vec = (uintptr_t(out) % 4 == 0 && out_stride % 2 == 0 && kv_rank % 2 == 0) ? 1 : 0;
-  const dim3 grid((n_rows + n_entries * (p.tokens_here - 1)) / p.tokens_here, head_groups);
+  const dim3 grid((n_rows + n_entries * (p.tokens_here - 1)) / p.tokens_here, head_groups, n_slices);
   if (single_rows) launch_latent_attention_of<true>(kv_rank, p, grid, stream);
   else launch_latent_attention_of<false>(kv_rank, p, grid, stream);
+  if (n_slices > 1) {
+    const int status = launch_status();
+    if (status != R2_OK) return status;
+    r2_launch(latent_merge_kernel, dim3(n_entries * n_heads), dim3(128), size_t(0), stream, (const float*)parts, n_slices, kv_rank, n_heads, sinks,
+              (bf16*)out, out_stride);
+  }
   return launch_status();
 }

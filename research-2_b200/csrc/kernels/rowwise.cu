@@ -684,66 +684,123 @@ rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int head_di
   }
 }
 
-// The same after an RMS norm of every head (one warp per head: the first n_q_heads heads take the gain q_w, the others k_w,
-// both of head_dim numbers; null: no norm), with cos and sin times `magnitude`: x / sqrt(mean(x^2) + eps) * w, then the
-// rotation, all in float and rounded once on the way out.
-constexpr int NORM_ROTATE_MAX_DIM = 512;
+// The same after an RMS norm of every head, with cos and sin times `magnitude`: x / sqrt(mean(x^2) + eps) * w, then the rotation,
+// all in float and rounded once on the way out. One warp per unit of work and eight units a CTA (grid: rows x ceil(units / 8)),
+// so that a decode step's few rows still spread over many SMs: units 0 .. n_heads - 1 are the heads (the first n_q_heads take the
+// gain q_w, the others k_w; null: no norm), and a key head's warp also puts the turned key into the row's cache slot; with a
+// cache, units n_heads .. n_heads + n_kv_heads - 1 copy the value heads to the slot. The row's cosines and sines are made once
+// a CTA, in shared memory, for all its heads. `vec`: neighbouring pairs of elements may go as one access (even sizes and strides).
+constexpr int NORM_ROTATE_MAX_DIM = 512, NORM_ROTATE_WARPS = 8;
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(NORM_ROTATE_WARPS * 32)
 norm_rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int n_q_heads, int head_dim, int half, const float* __restrict__ freq,
                         float magnitude, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                         const int32_t* __restrict__ positions, T* __restrict__ k_cache, T* __restrict__ v_cache,
                         const int32_t* __restrict__ slot_mapping, int k_col, int v_col, int n_kv_heads, int v_head_dim, int page_size,
-                        long long page_stride, int n_pages) {
+                        long long page_stride, int n_pages, int vec) {
   pdl_launch_dependents();
-  pdl_wait();
-  __shared__ float stage[4][NORM_ROTATE_MAX_DIM];
+  __shared__ float stage[NORM_ROTATE_WARPS][NORM_ROTATE_MAX_DIM];
+  __shared__ float cs_s[NORM_ROTATE_MAX_DIM / 2], sn_s[NORM_ROTATE_MAX_DIM / 2];
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int unit = blockIdx.y * NORM_ROTATE_WARPS + warp;
+  const int n_units = n_heads + (k_cache != nullptr ? n_kv_heads : 0);
+  // what no earlier kernel writes: the position and its angles, the slot
   const float p = float(positions[t]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cs;
+    sincosf(p * freq[i], &sn, &cs);
+    sn_s[i] = sn * magnitude;
+    cs_s[i] = cs * magnitude;
+  }
+  size_t page_at = 0;   // where the slot's page begins, and the slot's place in it
+  int off = 0;
+  bool has_slot = false;
+  if (k_cache != nullptr) {
+    const int slot = slot_mapping[t];
+    const int page = slot / page_size;
+    off = slot % page_size;
+    has_slot = slot >= 0 && page < n_pages;   // never write outside the pool
+    page_at = size_t(page) * page_stride;
+  }
+  __syncthreads();
+  pdl_wait();
+  if (unit >= n_units) return;
   T* row = buf + size_t(t) * row_stride;
+  if (unit >= n_heads) {   // a value head: its copy into the cache
+    if (!has_slot) return;
+    const int h = unit - n_heads;
+    const T* vs = row + v_col + size_t(h) * v_head_dim;
+    T* dst = v_cache + page_at + (size_t(h) * page_size + off) * v_head_dim;
+    if (vec && v_head_dim % 2 == 0) {
+      for (int d = 2 * lane; d < v_head_dim; d += 64) {
+        const float2 v = load2(vs + d);
+        store2(dst + d, v.x, v.y);
+      }
+    } else {
+      for (int d = lane; d < v_head_dim; d += 32) dst[d] = vs[d];
+    }
+    return;
+  }
   float* mine = stage[warp];
-  for (int head = warp; head < n_heads; head += 4) {
-    T* x = row + size_t(head) * head_dim;
-    const float* w = head < n_q_heads ? q_w : k_w;
-    float sq = 0.f;
+  T* x = row + size_t(unit) * head_dim;
+  const float* w = unit < n_q_heads ? q_w : k_w;
+  // a key head's place in the cache (the key heads are the n_kv_heads heads from column k_col on)
+  T* kdst = nullptr;
+  if (has_slot) {
+    const long long col = (long long)unit * head_dim - k_col;
+    if (col >= 0 && col < (long long)n_kv_heads * head_dim) kdst = k_cache + page_at + (size_t(col / head_dim) * page_size + off) * head_dim;
+  }
+  float sq = 0.f;
+  if (vec) {
+    for (int d = 2 * lane; d < head_dim; d += 64) {
+      const float2 v = load2(x + d);
+      mine[d] = v.x;
+      mine[d + 1] = v.y;
+      sq = fmaf(v.x, v.x, fmaf(v.y, v.y, sq));
+    }
+  } else {
     for (int d = lane; d < head_dim; d += 32) {
       const float v = to_float(x[d]);
       mine[d] = v;
       sq = fmaf(v, v, sq);
     }
-    sq = warp_sum(sq);
-    const float inv = w != nullptr ? 1.f / sqrtf(sq / float(head_dim) + eps) : 1.f;
-    __syncwarp();
-    for (int i = lane; i < head_dim - half; i += 32) {
+  }
+  sq = warp_sum(sq);
+  const float inv = w != nullptr ? 1.f / sqrtf(sq / float(head_dim) + eps) : 1.f;
+  __syncwarp();
+  // the value at dimension d after its norm
+  auto normed = [&](int d) { return w != nullptr ? mine[d] * inv * w[d] : mine[d]; };
+  if (vec) {   // half and head_dim are even: two neighbouring pairs (or two passing dimensions) a step
+    for (int i = 2 * lane; i < head_dim - half; i += 64) {
       if (i < half) {
-        float sn, cs;
-        sincosf(p * freq[i], &sn, &cs);
-        sn *= magnitude;
-        cs *= magnitude;
-        const float u = mine[i] * inv * (w != nullptr ? w[i] : 1.f), v = mine[i + half] * inv * (w != nullptr ? w[i + half] : 1.f);
-        x[i] = from_float<T>(u * cs - v * sn);
-        x[i + half] = from_float<T>(v * cs + u * sn);
-      } else if (w != nullptr) {
+        const float u0 = normed(i), u1 = normed(i + 1), v0 = normed(i + half), v1 = normed(i + half + 1);
+        const float a0 = u0 * cs_s[i] - v0 * sn_s[i], a1 = u1 * cs_s[i + 1] - v1 * sn_s[i + 1];
+        const float b0 = v0 * cs_s[i] + u0 * sn_s[i], b1 = v1 * cs_s[i + 1] + u1 * sn_s[i + 1];
+        store2(x + i, a0, a1);
+        store2(x + i + half, b0, b1);
+        if (kdst != nullptr) { store2(kdst + i, a0, a1); store2(kdst + i + half, b0, b1); }
+      } else {
         const int d = i + half;   // the dimensions after the rotated ones pass with their norm alone
-        x[d] = from_float<T>(mine[d] * inv * w[d]);
+        const float a0 = normed(d), a1 = normed(d + 1);
+        if (w != nullptr) store2(x + d, a0, a1);
+        if (kdst != nullptr) store2(kdst + d, a0, a1);
       }
     }
-    __syncwarp();
+    return;
   }
-  if (k_cache == nullptr) return;
-  __syncthreads();
-  const int slot = slot_mapping[t];
-  const int page = slot / page_size, off = slot % page_size;
-  if (slot < 0 || page >= n_pages) return;  // never write outside the pool
-  const T* ks = row + k_col;
-  const T* vs = row + v_col;
-  for (int i = threadIdx.x; i < n_kv_heads * head_dim; i += blockDim.x) {
-    const int h = i / head_dim, d = i % head_dim;
-    k_cache[size_t(page) * page_stride + (size_t(h) * page_size + off) * head_dim + d] = ks[i];
-  }
-  for (int i = threadIdx.x; i < n_kv_heads * v_head_dim; i += blockDim.x) {
-    const int h = i / v_head_dim, d = i % v_head_dim;
-    v_cache[size_t(page) * page_stride + (size_t(h) * page_size + off) * v_head_dim + d] = vs[i];
+  for (int i = lane; i < head_dim - half; i += 32) {
+    if (i < half) {
+      const float u = normed(i), v = normed(i + half);
+      const T a = from_float<T>(u * cs_s[i] - v * sn_s[i]), b = from_float<T>(v * cs_s[i] + u * sn_s[i]);
+      x[i] = a;
+      x[i + half] = b;
+      if (kdst != nullptr) { kdst[i] = a; kdst[i + half] = b; }
+    } else {
+      const int d = i + half;
+      const T a = w != nullptr ? from_float<T>(mine[d] * inv * w[d]) : x[d];
+      if (w != nullptr) x[d] = a;
+      if (kdst != nullptr) kdst[d] = a;
+    }
   }
 }
 
@@ -786,14 +843,20 @@ extern "C" int r2_rotate_half(void* buf, int row_stride, int n_rows, int n_heads
   if (normed || magnitude != 1.f) {
     if (head_dim > NORM_ROTATE_MAX_DIM || n_q_heads < 0 || n_q_heads > n_heads) return R2_BAD_SHAPE;
     if ((n_q_heads > 0 && normed && q_norm_w == nullptr) || (n_q_heads < n_heads && normed && k_norm_w == nullptr)) return R2_BAD_SHAPE;
+    const dim3 grid2(n_rows, (n_heads + (k_cache != nullptr ? n_kv_heads : 0) + NORM_ROTATE_WARPS - 1) / NORM_ROTATE_WARPS);
+    // neighbouring elements as one access: every size, stride and column that an address is made of is even
+    const bool pairs_ok = head_dim % 2 == 0 && half % 2 == 0 && row_stride % 2 == 0 &&
+                          (k_cache == nullptr || (k_col % 2 == 0 && v_col % 2 == 0 && v_head_dim % 2 == 0 && page_stride % 2 == 0));
     if (dtype == R2_F32) {
-      r2_launch(norm_rotate_half_kernel<float>, dim3(n_rows), dim3(128), size_t(0), stream, (float*)buf, row_stride, n_heads, n_q_heads, head_dim,
+      const bool vec = pairs_ok && pair_aligned((const float*)buf) && (k_cache == nullptr || (pair_aligned((const float*)k_cache) && pair_aligned((const float*)v_cache)));
+      r2_launch(norm_rotate_half_kernel<float>, grid2, dim3(NORM_ROTATE_WARPS * 32), size_t(0), stream, (float*)buf, row_stride, n_heads, n_q_heads, head_dim,
                 half, inv_freq, magnitude, q_norm_w, k_norm_w, norm_eps, positions, (float*)k_cache, (float*)v_cache, slot_mapping, k_col, v_col,
-                n_kv_heads, v_head_dim, page_size, page_stride, n_pages);
+                n_kv_heads, v_head_dim, page_size, page_stride, n_pages, int(vec));
     } else if (dtype == R2_BF16) {
-      r2_launch(norm_rotate_half_kernel<bf16>, dim3(n_rows), dim3(128), size_t(0), stream, (bf16*)buf, row_stride, n_heads, n_q_heads, head_dim,
+      const bool vec = pairs_ok && pair_aligned((const bf16*)buf) && (k_cache == nullptr || (pair_aligned((const bf16*)k_cache) && pair_aligned((const bf16*)v_cache)));
+      r2_launch(norm_rotate_half_kernel<bf16>, grid2, dim3(NORM_ROTATE_WARPS * 32), size_t(0), stream, (bf16*)buf, row_stride, n_heads, n_q_heads, head_dim,
                 half, inv_freq, magnitude, q_norm_w, k_norm_w, norm_eps, positions, (bf16*)k_cache, (bf16*)v_cache, slot_mapping, k_col, v_col,
-                n_kv_heads, v_head_dim, page_size, page_stride, n_pages);
+                n_kv_heads, v_head_dim, page_size, page_stride, n_pages, int(vec));
     } else {
       return R2_BAD_DTYPE;
     }

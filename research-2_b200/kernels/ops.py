@@ -222,6 +222,17 @@ def use_decode_mma(on: bool, head_dim: int = 64) -> bool:
     return bool(_lib_for_head_dim("attention_decode", head_dim).r2_attention_decode_set_mma(int(bool(on))))
 
 
+_latent_slices = os.environ.get("R2_LATENT_SLICES", "1") != "0"
+
+
+def use_latent_slices(on: bool) -> bool:
+    """Whether a decode step's attention over a cache of latents cuts a token's keys over several CTAs (and merges them in a
+    second launch); returns the old setting."""
+    global _latent_slices
+    old, _latent_slices = _latent_slices, bool(on)
+    return old
+
+
 def use_fast_attention(on: bool) -> bool:
     """Switch bfloat16 attention between the fast kernels and the general CUDA-core one."""
     global _fast_attention
@@ -1218,11 +1229,20 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
             and not sink and gate is None and softcap == 0.0 and head_gate is None and head_dim <= 256 and v_head_dim <= head_dim):
         # a cache of latents: every head reads the same rows, so a tile's rows are (token, head) pairs (mma.sync)
         _need(q_start, "q_start", torch.int32, 1)
+        single_rows = decode_only and n == q_start.shape[0] - 1
+        n_slices, ws = 1, _workspace(q.device)
+        if single_rows and _latent_slices:
+            # a decode step's token walks all its keys: cut them over enough CTAs to fill the SMs twice (a tile is 64 keys)
+            tiles = -(-(min(max_context, window) if window > 0 else max_context) // 64)
+            ctas = n * -(-n_heads // 16)
+            n_slices = max(1, min(tiles, 16, -(-2 * sm_count(q.device) // ctas)))
         status = _lib("latent_attention").r2_latent_attention(
             _p(q), _rows(q, "q"), _p(out), _rows(out, "out"), _p(k_cache), C.c_longlong(page_stride), page_size, n_pages,
             _p(block_tables), block_tables.shape[1], _p(q_start), _p(positions), _p(seq_lens), q_start.shape[0] - 1, n, n_heads,
-            head_dim, v_head_dim, C.c_float(scale), window, int(_exact_weights), int(decode_only and n == q_start.shape[0] - 1), _p(sinks),
-            _stream())
+            head_dim, v_head_dim, C.c_float(scale), window, int(_exact_weights), int(single_rows), _p(sinks), n_slices, _p(ws.floats),
+            C.c_longlong(ws.floats.numel()), _stream())
+        if n_slices > 1:
+            count_launches(1)  # the merge kernel
         _check(status, "paged_attention (latents)")
         _used("latent_attention")
         return out
@@ -1237,7 +1257,7 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     return out
 
 
-def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Tensor, slot_mapping: torch.Tensor,
+def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor | None, v_new: torch.Tensor | None, slot_mapping: torch.Tensor | None,
                            k_cache: torch.Tensor, v_cache: torch.Tensor, page_stride: int, page_size: int, n_pages: int,
                            block_tables: torch.Tensor, row_entry: torch.Tensor, positions: torch.Tensor,
                            seq_lens: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, scale: float,
@@ -1247,21 +1267,27 @@ def decode_attention_fused(q: torch.Tensor, k_new: torch.Tensor, v_new: torch.Te
     """Decode attention in ONE launch for a batch in which every row is an entry of its own: the
     kernel writes the new keys and values to their cache slots, and the slice that finishes last
     merges all slices of its row. Returns None when it does not take the case (the caller then writes
-    the cache and calls `paged_attention`). `keep_first`, `sink`, `gate`, `softcap`, `sinks` and `head_gate` as in `paged_attention`;
+    the cache and calls `paged_attention`). With `k_new` None nothing is written: the rows read a cache that already holds
+    their own position (a layer that reads the keys and values another layer wrote in this step).
+    `keep_first`, `sink`, `gate`, `softcap`, `sinks` and `head_gate` as in `paged_attention`;
     `exact_weights` carries the softmax's weights into the second product as two bfloat16 terms."""
     group = n_heads // max(n_kv_heads, 1)
     if not (_fast_attention and _fused_decode and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
             and 1 <= group <= 8 and head_dim % 16 == 0):
         return None
     _need(q, "q", dim=2)
-    _need(k_new, "k_new", torch.bfloat16, 2)
-    _need(v_new, "v_new", torch.bfloat16, 2)
-    _need(slot_mapping, "slot_mapping", torch.int32, 1)
     _need(block_tables, "block_tables", torch.int32, 2)
     n = q.shape[0]
-    stride = _rows(k_new, "k_new")
-    if _rows(v_new, "v_new") != stride or k_new.shape != (n, n_kv_heads * head_dim) or slot_mapping.shape[0] < n:
-        raise KernelError("decode attention: the new keys and values do not fit the rows")
+    stride = 0
+    if k_new is not None:
+        _need(k_new, "k_new", torch.bfloat16, 2)
+        _need(v_new, "v_new", torch.bfloat16, 2)
+        _need(slot_mapping, "slot_mapping", torch.int32, 1)
+        stride = _rows(k_new, "k_new")
+        if _rows(v_new, "v_new") != stride or k_new.shape != (n, n_kv_heads * head_dim) or slot_mapping.shape[0] < n:
+            raise KernelError("decode attention: the new keys and values do not fit the rows")
+    else:
+        v_new = slot_mapping = None
     if window > 0:
         max_context = min(max_context, window + keep_first)   # what a row reads at most
     slices = decode_slices(n, n_kv_heads, max_context, q.device)

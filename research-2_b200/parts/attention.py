@@ -271,13 +271,13 @@ class RotaryWindowAttention:
     capturable = True
 
     def _inner(self, h, ctx, cache, writes_cache):
-        if writes_cache != self.own_kv:
-            raise ValueError("attention: a layer with keys and values of its own writes its cache member, one without reads another's")
+        if writes_cache and not self.own_kv:
+            raise ValueError("attention: a layer without keys and values of its own reads a cache member that another layer writes")
         proj = ops.linear(h, self.w_in, None, w_is_nk=True)
         gate = ops.small_linear(h, self.w_gate, None) if self.w_gate is not None else None
         at = self.q_width + self.k_width
         q, k, v = proj[:, : self.q_width], proj[:, self.q_width: at], proj[:, at:]
-        fused_decode = writes_cache and ctx.decode_only and self.v_head_dim == self.head_dim
+        fused_decode = ctx.decode_only and self.v_head_dim == self.head_dim
         turned = self.n_heads + (self.n_kv_heads if self.own_kv else 0)    # the heads that are normed and rotated
         norms = dict(q_norm=self.q_norm, k_norm=self.k_norm, n_q_heads=self.n_heads, norm_eps=self.norm_eps or 0.0,
                      magnitude=self.rot_magnitude)
@@ -290,16 +290,18 @@ class RotaryWindowAttention:
         elif self.rot_dims or self.q_norm is not None:
             ops.rotate_half(proj, turned, self.head_dim, self.rot_dims, self.inv_freq, ctx.positions, **norms)
         if fused_decode:
-            # one new token per row: the kernel puts the new key and value into the cache itself
+            # one new token per row: the kernel puts the new key and value into the cache itself (a layer that reads another's
+            # cache member hands it none: that layer wrote them earlier in this step)
             mixed = ops.decode_attention_fused(
-                q, k, v, ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride, cache.page_size, cache.n_pages,
-                ctx.block_tables[cache.group], ctx.row_entry, ctx.positions, ctx.seq_lens, self.n_heads, self.n_kv_heads,
-                self.head_dim, self.scale, self.window, ctx.max_context, exact_weights=ops.exact_weights(), softcap=self.softcap,
+                q, k if writes_cache else None, v if writes_cache else None, ctx.slot_mapping[cache.group], cache.k, cache.v, cache.page_stride,
+                cache.page_size, cache.n_pages, ctx.block_tables[cache.group], ctx.row_entry, ctx.positions, ctx.seq_lens, self.n_heads,
+                self.n_kv_heads, self.head_dim, self.scale, self.window, ctx.max_context, exact_weights=ops.exact_weights(), softcap=self.softcap,
                 sinks=self.sinks, head_gate=gate)
             if mixed is not None:
                 return mixed
-            ops.kv_write(k, v, cache.k, cache.v, ctx.slot_mapping[cache.group], self.n_kv_heads, self.head_dim,
-                         cache.page_size, cache.page_stride, cache.n_pages, v_head_dim=self.v_head_dim)
+            if writes_cache:
+                ops.kv_write(k, v, cache.k, cache.v, ctx.slot_mapping[cache.group], self.n_kv_heads, self.head_dim,
+                             cache.page_size, cache.page_stride, cache.n_pages, v_head_dim=self.v_head_dim)
         return ops.paged_attention(
             q, cache.k, cache.v, cache.page_stride, cache.page_size, cache.n_pages, ctx.block_tables[cache.group],
             ctx.row_entry, ctx.positions, ctx.seq_lens, self.n_heads, self.n_kv_heads, self.head_dim, self.scale,
@@ -367,8 +369,8 @@ class LatentAttention:
             if len(have) != len(want) or any(w is not None and w != g for w, g in zip(want, have)):
                 raise ValueError(f"latent attention: {name} {have} does not fit {H} heads of {self.head_dim} + {self.rot_dim} "
                                  f"(values {self.v_head_dim}) over a latent of {self.kv_rank}")
-        if self.row > 256:
-            raise ValueError(f"latent attention: cache rows of {self.row} numbers exceed the kernels' 256")
+        if self.row > 1024:
+            raise ValueError(f"latent attention: cache rows of {self.row} numbers exceed the kernels' 1,024")
         # one product for everything that reads the layer's input: [queries or their latent | latent and key part | gate]
         self.gated = weights.get("w_gate") is not None
         stacked = [weights["w_dq"] if self.q_rank else weights["w_q"], weights["w_dkv"]] + ([weights["w_gate"]] if self.gated else [])

@@ -27,6 +27,7 @@ def main() -> int:
     ap.add_argument("--window", type=int, default=256)
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--head-linear", action="store_true")
+    ap.add_argument("--sinks", action="store_true", help="a learned term per head in the softmax's denominator")
     ap.add_argument("--time", action="store_true")
     args = ap.parse_args()
     dev, h, c, row, page = "cuda:0", args.heads, args.rank, args.rank + args.rot, args.page_size
@@ -52,11 +53,12 @@ def main() -> int:
         positions = torch.arange(length - args.rows, length, dtype=torch.int32, device=dev).repeat(args.entries)
         seq_lens = i32([length] * args.entries)
         n_tiles = args.entries * -(-args.rows // 64)
+        sinks = torch.randn(h, device=dev) if args.sinks else None
 
         def fn():
             ops.paged_attention(queries, cache, cache, page * row, page, args.entries * pages_each, tables, row_entry, positions, seq_lens,
                                 h, 1, row, row ** -0.5, args.window, out=mixed, decode_only=args.rows == 1, max_context=length,
-                                q_start=q_start, n_tiles=n_tiles, v_head_dim=c, values_in_keys=True)
+                                q_start=q_start, n_tiles=n_tiles, v_head_dim=c, values_in_keys=True, sinks=sinks)
     if args.time:
         print(f"{time_in_graph(fn):.1f} us a launch")
         return 0
