@@ -702,7 +702,6 @@ norm_rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int n_
   __shared__ float stage[NORM_ROTATE_WARPS][NORM_ROTATE_MAX_DIM];
   __shared__ float cs_s[NORM_ROTATE_MAX_DIM / 2], sn_s[NORM_ROTATE_MAX_DIM / 2];
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int unit = blockIdx.y * NORM_ROTATE_WARPS + warp;
   const int n_units = n_heads + (k_cache != nullptr ? n_kv_heads : 0);
   // what no earlier kernel writes: the position and its angles, the slot
   const float p = float(positions[t]);
@@ -724,10 +723,12 @@ norm_rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int n_
   }
   __syncthreads();
   pdl_wait();
-  if (unit >= n_units) return;
   T* row = buf + size_t(t) * row_stride;
+  float* mine = stage[warp];
+  // the CTAs of a row share its units; with many rows a row has one CTA, whose warps take the units in turn
+  for (int unit = blockIdx.y * NORM_ROTATE_WARPS + warp; unit < n_units; unit += gridDim.y * NORM_ROTATE_WARPS) {
   if (unit >= n_heads) {   // a value head: its copy into the cache
-    if (!has_slot) return;
+    if (!has_slot) continue;
     const int h = unit - n_heads;
     const T* vs = row + v_col + size_t(h) * v_head_dim;
     T* dst = v_cache + page_at + (size_t(h) * page_size + off) * v_head_dim;
@@ -739,9 +740,9 @@ norm_rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int n_
     } else {
       for (int d = lane; d < v_head_dim; d += 32) dst[d] = vs[d];
     }
-    return;
+    continue;
   }
-  float* mine = stage[warp];
+  __syncwarp();   // (the warp's staging row may still be read from its unit before)
   T* x = row + size_t(unit) * head_dim;
   const float* w = unit < n_q_heads ? q_w : k_w;
   // a key head's place in the cache (the key heads are the n_kv_heads heads from column k_col on)
@@ -786,7 +787,7 @@ norm_rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int n_
         if (kdst != nullptr) store2(kdst + d, a0, a1);
       }
     }
-    return;
+    continue;
   }
   for (int i = lane; i < head_dim - half; i += 32) {
     if (i < half) {
@@ -801,6 +802,7 @@ norm_rotate_half_kernel(T* __restrict__ buf, int row_stride, int n_heads, int n_
       if (w != nullptr) x[d] = a;
       if (kdst != nullptr) kdst[d] = a;
     }
+  }
   }
 }
 
@@ -843,7 +845,8 @@ extern "C" int r2_rotate_half(void* buf, int row_stride, int n_rows, int n_heads
   if (normed || magnitude != 1.f) {
     if (head_dim > NORM_ROTATE_MAX_DIM || n_q_heads < 0 || n_q_heads > n_heads) return R2_BAD_SHAPE;
     if ((n_q_heads > 0 && normed && q_norm_w == nullptr) || (n_q_heads < n_heads && normed && k_norm_w == nullptr)) return R2_BAD_SHAPE;
-    const dim3 grid2(n_rows, (n_heads + (k_cache != nullptr ? n_kv_heads : 0) + NORM_ROTATE_WARPS - 1) / NORM_ROTATE_WARPS);
+    // few rows (a decode step): a row's units spread over several CTAs; many rows: one CTA a row, its cosines and sines made once
+    const dim3 grid2(n_rows, n_rows >= 512 ? 1 : (n_heads + (k_cache != nullptr ? n_kv_heads : 0) + NORM_ROTATE_WARPS - 1) / NORM_ROTATE_WARPS);
     // neighbouring elements as one access: every size, stride and column that an address is made of is even
     const bool pairs_ok = head_dim % 2 == 0 && half % 2 == 0 && row_stride % 2 == 0 &&
                           (k_cache == nullptr || (k_col % 2 == 0 && v_col % 2 == 0 && v_head_dim % 2 == 0 && page_stride % 2 == 0));
