@@ -845,8 +845,11 @@ extern "C" int r2_rotate_half(void* buf, int row_stride, int n_rows, int n_heads
   if (normed || magnitude != 1.f) {
     if (head_dim > NORM_ROTATE_MAX_DIM || n_q_heads < 0 || n_q_heads > n_heads) return R2_BAD_SHAPE;
     if ((n_q_heads > 0 && normed && q_norm_w == nullptr) || (n_q_heads < n_heads && normed && k_norm_w == nullptr)) return R2_BAD_SHAPE;
-    // few rows (a decode step): a row's units spread over several CTAs; many rows: one CTA a row, its cosines and sines made once
-    const dim3 grid2(n_rows, n_rows >= 512 ? 1 : (n_heads + (k_cache != nullptr ? n_kv_heads : 0) + NORM_ROTATE_WARPS - 1) / NORM_ROTATE_WARPS);
+    // few rows (a decode step): a row's units spread over several CTAs; a prompt step's rows: one CTA a row, its cosines and sines made
+    // once (11.8 against 14.4 us at 2,048 rows of 18 units); beyond that the SMs are full either way and the spread form is the faster
+    // again (230 against 372 us at 65,536 rows)
+    const bool one_cta_a_row = n_rows >= 512 && n_rows < 16384;
+    const dim3 grid2(n_rows, one_cta_a_row ? 1 : (n_heads + (k_cache != nullptr ? n_kv_heads : 0) + NORM_ROTATE_WARPS - 1) / NORM_ROTATE_WARPS);
     // neighbouring elements as one access: every size, stride and column that an address is made of is even
     const bool pairs_ok = head_dim % 2 == 0 && half % 2 == 0 && row_stride % 2 == 0 &&
                           (k_cache == nullptr || (k_col % 2 == 0 && v_col % 2 == 0 && v_head_dim % 2 == 0 && page_stride % 2 == 0));
