@@ -99,9 +99,9 @@ CASES = {
     ], eps=1e-5), "seed": 8, "std": 0.05, "page_size": 32},
     # heads and latents of 64 and more (the tensor-core kernels' shapes), pages of 4, a reader before and after a latent layer
     "d": {"config": model(128, 96, [
-        layer(attention(4, 2, 64, 64, 0.125, rot=(64, 20000.0, (2.0, 128, 16.0, 1.0))), moe(4, 2, 40, groups=(2, 2), scale=2.0)),
+        layer(attention(4, 2, 64, 64, 0.125, rot=(64, 30000.0, (2.0, 128, 16.0, 1.0))), moe(4, 2, 40, groups=(2, 2), scale=2.0)),
         layer(latent(2, 64, 32, 64, 96, 0.1, q_rank=48, rot=(32, 10000.0))),
-        layer(attention(2, 2, 64, 64, 0.11, rot=(64, 20000.0, (2.0, 128, 16.0, 1.0)), kv_from=0), moe(2, 1, 40, groups=(2, 1))),
+        layer(attention(2, 2, 64, 64, 0.11, rot=(64, 30000.0, (2.0, 128, 16.0, 1.0)), kv_from=0), moe(2, 1, 40, groups=(2, 1))),
     ], eps=1e-5, alpha=3.5, embedding_scale=0.7), "seed": 13, "std": 0.07, "page_size": 4},
 }
 
@@ -122,7 +122,7 @@ def random_case(seed: int) -> dict:
             rot_dim = rng.choice([2, 4, 8, 16, 32, 64])
             rot = None
             if rng.random() < 0.85:
-                rot = (rot_dim, rng.choice([100.0, 10000.0, 500000.0]))
+                rot = (rot_dim, rng.choice([100.0, 10000.0, 250000.0]))
                 if rng.random() < 0.4:
                     rot += ((rng.choice([2.0, 4.0, 16.0]), rng.choice([32, 128, 1024]), rng.choice([8.0, 32.0]), rng.choice([1.0, 2.0])),)
             dim = rng.choice([4, 8, 16, 24, 32, 64, 96, 128])
@@ -140,7 +140,7 @@ def random_case(seed: int) -> dict:
             rot = None
             if rng.random() < 0.85:
                 dims = rng.choice(list(range(2, dim + 1, 2))) if rng.random() < 0.4 else dim
-                rot = (dims, rng.choice([100.0, 20000.0, 1000000.0]))
+                rot = (dims, rng.choice([100.0, 30000.0, 1000000.0]))
                 if rng.random() < 0.6:
                     rot += ((rng.choice([2.0, 4.0, 16.0]), rng.choice([32, 128, 1024]), rng.choice([8.0, 32.0]), rng.choice([1.0, 2.0])),)
             mixer = attention(kv_heads * rng.choice([1, 1, 2, 3, 4, 8]), kv_heads, dim, rng.choice([dim, dim, 8, 16, 40, 64, 80]),
